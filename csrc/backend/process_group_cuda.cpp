@@ -1,0 +1,601 @@
+// CUDA data path of ProcessGroupMCCL: stream-ordered launches of the fused
+// collective kernels over the SymmetricArena.
+//
+// Ordering (replaces the reference's MTLSharedEvent fences,
+// reference csrc/metal/EventSync.mm:123-234):
+//   producer fence   cudaEventRecord(current stream) + cudaStreamWaitEvent(comm)
+//   kernel(s)        on the high-priority communication stream, one epoch each
+//   consumer release event recorded behind the kernels; Work::wait and the
+//                    CUDA-aware Future make consumers wait for it on-device
+// With MCCL_OVERLAP_COMM=0 the kernels run on the caller's stream instead.
+#include <ATen/cuda/CUDAContext.h>
+#include <ATen/cuda/CUDAEvent.h>
+#include <c10/cuda/CUDACachingAllocator.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda_runtime_api.h>
+
+#include "backend/process_group.h"
+#include "backend/tensor_checks.h"
+#include "common/log.h"
+#include "kernels/topk_api.h"
+
+namespace mccl {
+
+struct ProcessGroupMCCL::CudaState {
+  c10::DeviceIndex dev = 0;
+  std::unique_ptr<c10::cuda::CUDAStream> comm;
+  cudaStream_t poll_stream = nullptr;
+  std::unique_ptr<SymmetricArena> arena;
+  bool p2p = false;
+  std::string why_not;
+  at::cuda::CUDAEvent fence{cudaEventDisableTiming};
+  struct Pending {
+    uint32_t seq;
+    cudaEvent_t start, end;
+  };
+  std::deque<Pending> pending;
+  std::vector<cudaEvent_t> free_events;
+  std::mutex pending_mu;
+  uint32_t last_status[kern::kStatusWords] = {0};
+
+  cudaEvent_t get_event() {
+    if (!free_events.empty()) {
+      cudaEvent_t e = free_events.back();
+      free_events.pop_back();
+      return e;
+    }
+    cudaEvent_t e;
+    MCCL_CUDA_CHECK(cudaEventCreate(&e));
+    return e;
+  }
+  ~CudaState() {
+    c10::cuda::OptionalCUDAGuard g(dev);
+    for (auto& p : pending) {
+      cudaEventDestroy(p.start);
+      cudaEventDestroy(p.end);
+    }
+    for (auto e : free_events) cudaEventDestroy(e);
+    arena.reset();
+    if (poll_stream) cudaStreamDestroy(poll_stream);
+  }
+};
+
+std::string ProcessGroupMCCL::data_plane() const {
+  if (getSize() == 1) return "local";
+  if (!cuda_) return "uninitialised";
+  return cuda_->p2p ? "nvlink-p2p" : "host-staged";
+}
+
+void ProcessGroupMCCL::ensure_cuda(c10::DeviceIndex dev) {
+  std::lock_guard<std::mutex> g(cuda_mu_);
+  if (cuda_) {
+    MCCL_CHECK(cuda_->dev == dev, "this process group is bound to cuda:" << int(cuda_->dev)
+                                                                         << " but got a tensor on cuda:" << int(dev));
+    return;
+  }
+  c10::cuda::CUDAGuard guard(dev);
+  auto st = std::make_shared<CudaState>();
+  st->dev = dev;
+  st->comm = std::make_unique<c10::cuda::CUDAStream>(c10::cuda::getStreamFromPool(/*isHighPriority=*/true, dev));
+  MCCL_CUDA_CHECK(cudaStreamCreateWithFlags(&st->poll_stream, cudaStreamNonBlocking));
+
+  const int ws = getSize();
+  std::string local_reason;
+  if (options_->algo == "staged") {
+    local_reason = "MCCL_ALGO=staged";
+  } else if (ws > kern::kMaxWorld) {
+    local_reason = "world size " + std::to_string(ws) + " exceeds one NVLink domain of " + std::to_string(kern::kMaxWorld);
+  } else {
+    try {
+      st->arena = std::make_unique<SymmetricArena>(getRank(), ws, static_cast<size_t>(options_->arena_bytes));
+    } catch (const std::exception& e) {
+      local_reason = e.what();
+    }
+  }
+  const auto timeout = std::chrono::milliseconds(env_int("MCCL_CONNECT_TIMEOUT_MS", 30000));
+  // Round 1: publish handles (or the reason there is none).
+  std::string mine = st->arena ? ("H" + st->arena->export_handle()) : ("X" + local_reason);
+  auto all = rendezvous_->exchange("arena", mine, timeout);
+  if (local_reason.empty()) {
+    std::vector<std::string> handles(ws);
+    for (int r = 0; r < ws; ++r) {
+      if (all[r].empty() || all[r][0] != 'H') {
+        local_reason = "rank " + std::to_string(r) + " has no arena: " + (all[r].empty() ? "" : all[r].substr(1));
+        break;
+      }
+      handles[r] = all[r].substr(1);
+    }
+    if (local_reason.empty()) local_reason = st->arena->open_peers(handles);
+  }
+  // Round 2: agree. One failure anywhere puts every rank on the host-staged path.
+  auto verdicts = rendezvous_->exchange("arena_ok", local_reason.empty() ? "ok" : local_reason, timeout);
+  st->p2p = true;
+  for (int r = 0; r < ws; ++r)
+    if (verdicts[r] != "ok") {
+      st->p2p = false;
+      st->why_not = "rank " + std::to_string(r) + ": " + verdicts[r];
+      break;
+    }
+  if (!st->p2p) {
+    st->arena.reset();
+    MCCL_WARN("rank %d: peer-memory data plane unavailable (%s); CUDA collectives are staged through host memory",
+              getRank(), st->why_not.c_str());
+    ensure_transport();
+  } else {
+    MCCL_INFO("rank %d: NVLink peer arena mapped on %d ranks (%lld MiB x2 per rank)", getRank(), ws,
+              (long long)(options_->arena_bytes >> 20));
+  }
+  cuda_ = std::move(st);
+}
+
+void ProcessGroupMCCL::poll_device() {
+  std::unique_lock<std::mutex> g(cuda_mu_, std::try_to_lock);
+  if (!g.owns_lock() || !cuda_) return;
+  CudaState& cs = *cuda_;
+  c10::cuda::OptionalCUDAGuard guard(cs.dev);
+  // 1. finished collectives -> metrics + watchdog
+  {
+    std::lock_guard<std::mutex> pg(cs.pending_mu);
+    while (!cs.pending.empty()) {
+      auto& p = cs.pending.front();
+      cudaError_t q = cudaEventQuery(p.end);
+      if (q == cudaErrorNotReady) {
+        cudaGetLastError();
+        break;
+      }
+      float ms = 0.f;
+      if (q == cudaSuccess && cudaEventElapsedTime(&ms, p.start, p.end) != cudaSuccess) {
+        cudaGetLastError();
+        ms = 0.f;
+      }
+      metrics_.record_phase(p.seq, Metrics::Phase::NETWORK, ms);
+      metrics_.op_end_timed(p.seq, ms);
+      watchdog_->complete(p.seq);
+      cs.free_events.push_back(p.start);
+      cs.free_events.push_back(p.end);
+      cs.pending.pop_front();
+    }
+  }
+  // 2. device status block (bounded waits that gave up)
+  if (cs.arena && !poisoned_.load()) {
+    uint32_t st[kern::kStatusWords] = {0};
+    try {
+      cs.arena->read_status(st, cs.poll_stream);
+    } catch (const std::exception& e) {
+      g.unlock();
+      poison(std::string("device status read failed: ") + e.what(), true);
+      return;
+    }
+    if (st[0] != kern::ERR_NONE) {
+      std::memcpy(cs.last_status, st, sizeof(st));
+      std::ostringstream o;
+      o << "device-side wait timed out: arena epoch " << st[1] << " phase " << st[2] << " waiting for rank " << st[3]
+        << " (limit " << options_->device_wait_us << " us)";
+      g.unlock();
+      metrics_.record_error();
+      poison(o.str(), /*tell_peers=*/true);
+    }
+  }
+}
+
+void ProcessGroupMCCL::device_health_check() {
+  poll_device();
+  if (poisoned_.load()) throw MCCLError("collective failed: " + poison_reason());
+}
+
+namespace {
+
+struct LaunchScope {
+  // Orders the communication stream behind the caller's stream and picks the
+  // stream the kernels go to.
+  c10::cuda::CUDAStream stream;
+  LaunchScope(c10::cuda::CUDAStream cur, c10::cuda::CUDAStream comm, at::cuda::CUDAEvent& fence, bool overlap)
+      : stream(overlap ? comm : cur) {
+    if (overlap) {
+      fence.record(cur);
+      fence.block(comm);
+    }
+  }
+};
+
+double ms_since(std::chrono::steady_clock::time_point t0) {
+  return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+}
+
+}  // namespace
+
+#define MCCL_LAUNCH_CHECK(expr)                                                       \
+  do {                                                                                \
+    cudaError_t _le = (expr);                                                         \
+    if (_le != cudaSuccess) {                                                         \
+      cudaGetLastError();                                                             \
+      throw DeviceError(std::string(#expr) + ": " + cudaGetErrorString(_le));         \
+    }                                                                                 \
+  } while (0)
+
+// Shared prologue/epilogue of every arena collective.
+struct CudaPath {
+  ProcessGroupMCCL& pg;
+  ProcessGroupMCCL::CudaState& cs;
+  c10::intrusive_ptr<WorkMCCL> work;
+  uint32_t seq;
+  c10::cuda::CUDAStream stream;
+  cudaEvent_t ev_start = nullptr, ev_end = nullptr;
+  bool skip = false;
+
+  CudaPath(ProcessGroupMCCL& pg_, c10d::OpType op, const char* name, uint64_t bytes, std::vector<at::Tensor> outs,
+           c10::DeviceIndex dev)
+      : pg(pg_), cs(*pg_.cuda_), seq(pg_.next_seq()), stream(c10::cuda::getCurrentCUDAStream(dev)) {
+    if (pg.health_) pg.health_->check_now();  // learn about dead peers before launching
+    pg.check_alive(name);
+    work = c10::make_intrusive<WorkMCCL>(pg.getRank(), op, seq, name, std::move(outs), /*stream_mode=*/true, dev);
+    pg.metrics_.op_start(seq, name, bytes);
+    pg.watchdog_->watch(seq, name);
+    auto t0 = std::chrono::steady_clock::now();
+    LaunchScope scope(c10::cuda::getCurrentCUDAStream(dev), *cs.comm, cs.fence, pg.options_->overlap_comm);
+    stream = scope.stream;
+    pg.metrics_.record_phase(seq, Metrics::Phase::SYNC, ms_since(t0));
+    pg.metrics_.op_execute_start(seq);
+    pg.watchdog_->touch(seq);
+    {
+      std::lock_guard<std::mutex> g(cs.pending_mu);
+      ev_start = cs.get_event();
+      ev_end = cs.get_event();
+    }
+    MCCL_CUDA_CHECK(cudaEventRecord(ev_start, stream.stream()));
+    skip = pg.skip_next_launch_.exchange(false);
+  }
+
+  kern::CollParams params() {
+    kern::CollParams p;
+    std::memset(&p, 0, sizeof(p));
+    cs.arena->fill_params(p, cs.arena->next_epoch());
+    p.scale = 1.0f;
+    p.wait_ns = static_cast<unsigned long long>(pg.options_->device_wait_us) * 1000ull;
+    return p;
+  }
+
+  kern::LaunchCfg cfg(size_t bytes) {
+    kern::LaunchCfg c;
+    c.ctas = pg.tuner_.ctas_for(cs.arena->world_size(), bytes, static_cast<int>(pg.options_->comm_ctas));
+    return c;
+  }
+
+  void keep(const at::Tensor& t) {
+    if (t.defined() && t.is_cuda() && stream != c10::cuda::getCurrentCUDAStream(cs.dev))
+      c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), stream);
+  }
+
+  c10::intrusive_ptr<c10d::Work> finish(bool blocking = false) {
+    MCCL_CUDA_CHECK(cudaEventRecord(ev_end, stream.stream()));
+    {
+      std::lock_guard<std::mutex> g(cs.pending_mu);
+      cs.pending.push_back({seq, ev_start, ev_end});
+    }
+    ProcessGroupMCCL* self = &pg;
+    work->set_health_check([self] { self->device_health_check(); });
+    work->attach_stream(stream, blocking || pg.options_->blocking_wait);
+    return work;
+  }
+};
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::staged_via_host(
+    c10d::OpType op, std::vector<at::Tensor> cuda_tensors,
+    std::function<c10::intrusive_ptr<c10d::Work>(std::vector<at::Tensor>&)> fn, bool copy_back) {
+  std::vector<at::Tensor> host;
+  for (auto& t : cuda_tensors) host.push_back(t.to(at::kCPU));
+  auto w = fn(host);
+  w->wait();
+  if (copy_back)
+    for (size_t i = 0; i < host.size(); ++i) cuda_tensors[i].copy_(host[i]);
+  return completed_work(op, cuda_tensors, nullptr);
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allreduce(at::Tensor& t, c10d::ReduceOp::RedOpType op,
+                                                                float prescale) {
+  const auto dev = t.device().index();
+  ensure_cuda(dev);
+  if (!cuda_->p2p) {
+    return staged_via_host(
+        c10d::OpType::ALLREDUCE, {t},
+        [this, op](std::vector<at::Tensor>& h) {
+          c10d::AllreduceOptions o;
+          o.reduceOp = op;
+          return allreduce(h, o);
+        },
+        true);
+  }
+  c10::cuda::CUDAGuard guard(dev);
+  const int ws = getSize();
+  const kern::DType dt = to_kern_dtype(t.scalar_type());
+  kern::DType wire = dt;
+  const bool summing = op == c10d::ReduceOp::SUM || op == c10d::ReduceOp::AVG;
+  if (dt == kern::F32 && summing) {
+    if (options_->wire_dtype == "bf16") wire = kern::BF16;
+    else if (options_->wire_dtype == "fp16" || options_->compression == CompressionMode::FP16) wire = kern::F16;
+  }
+  const size_t esz = t.element_size();
+  const size_t wsz = kern::dtype_size(wire);
+  const int64_t n = t.numel();
+  CudaPath cp(*this, c10d::OpType::ALLREDUCE, "mccl:all_reduce", t.nbytes(), {t}, dev);
+  cp.keep(t);
+
+  // Segment so that every launch fits one parity buffer.
+  const size_t cap = cuda_->arena->parity_bytes();
+  int64_t seg_elems = static_cast<int64_t>(std::min(tuner_.segment_bytes(), cap * ws / (ws + 1)) / wsz);
+  seg_elems = std::max<int64_t>(seg_elems / 256 * 256, 256);
+  char* base = static_cast<char*>(t.data_ptr());
+  uint64_t sent = 0;
+  for (int64_t off = 0; off < n; off += seg_elems) {
+    const int64_t cnt = std::min(seg_elems, n - off);
+    const size_t wire_bytes = static_cast<size_t>(cnt) * wsz;
+    Variant v = tuner_.choose_allreduce(ws, wire_bytes);
+    if (options_->algo == "oneshot") v = Variant::ONESHOT;
+    if (options_->algo == "twoshot") v = Variant::TWOSHOT;
+    if (v == Variant::ONESHOT && kern::oneshot_arena_bytes(wire_bytes, ws) > cap) v = Variant::TWOSHOT;
+    MCCL_CHECK(kern::twoshot_arena_bytes(wire_bytes, ws) <= cap, "segment does not fit the arena");
+    kern::CollParams p = cp.params();
+    p.ctx[0].in = base + off * esz;
+    p.ctx[0].out = base + off * esz;
+    p.count = cnt;
+    p.op = to_kern_op(op);
+    p.scale = (op == c10d::ReduceOp::AVG ? 1.0f / ws : 1.0f) * prescale;
+    if (!cp.skip) {
+      if (v == Variant::ONESHOT)
+        MCCL_LAUNCH_CHECK(kern::launch_allreduce_oneshot(p, dt, wire, cp.cfg(wire_bytes), cp.stream.stream()));
+      else
+        MCCL_LAUNCH_CHECK(kern::launch_allreduce_twoshot(p, dt, wire, cp.cfg(wire_bytes), cp.stream.stream()));
+    }
+    sent += v == Variant::ONESHOT ? wire_bytes * (ws - 1) : 2 * wire_bytes * (ws - 1) / ws;
+    MCCL_DEBUG("allreduce seq=%u epoch=%u %s bytes=%zu wire=%d", cp.seq, p.seq,
+               v == Variant::ONESHOT ? "oneshot" : "twoshot", wire_bytes, int(wire));
+  }
+  metrics_.record_transport_bytes(sent, sent);
+  return cp.finish();
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_broadcast(at::Tensor& t, int root) {
+  const auto dev = t.device().index();
+  ensure_cuda(dev);
+  if (!cuda_->p2p) {
+    return staged_via_host(
+        c10d::OpType::BROADCAST, {t},
+        [this, root](std::vector<at::Tensor>& h) {
+          c10d::BroadcastOptions o;
+          o.rootRank = root;
+          return broadcast(h, o);
+        },
+        getRank() != root);
+  }
+  c10::cuda::CUDAGuard guard(dev);
+  CudaPath cp(*this, c10d::OpType::BROADCAST, "mccl:broadcast", t.nbytes(), {t}, dev);
+  cp.keep(t);
+  const size_t cap = cuda_->arena->parity_bytes() / 256 * 256;
+  const size_t nbytes = t.nbytes();
+  char* base = static_cast<char*>(t.data_ptr());
+  for (size_t off = 0; off < nbytes; off += cap) {
+    const size_t cnt = std::min(cap, nbytes - off);
+    kern::CollParams p = cp.params();
+    p.ctx[0].in = base + off;
+    p.ctx[0].out = base + off;
+    p.count = static_cast<int64_t>(cnt);
+    p.root = root;
+    if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_broadcast(p, cp.cfg(cnt), cp.stream.stream()));
+  }
+  if (getRank() == root) metrics_.record_transport_bytes(nbytes, 0);
+  else metrics_.record_transport_bytes(nbytes / getSize(), nbytes);
+  return cp.finish();
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allgather(at::Tensor& out_flat, const at::Tensor& in,
+                                                                std::vector<at::Tensor>* scatter_to) {
+  const auto dev = in.device().index();
+  ensure_cuda(dev);
+  const int ws = getSize();
+  if (!cuda_->p2p) {
+    at::Tensor hin = in.to(at::kCPU);
+    std::vector<at::Tensor> houts;
+    for (int r = 0; r < ws; ++r) houts.push_back(at::empty_like(hin));
+    std::vector<std::vector<at::Tensor>> ol{houts};
+    std::vector<at::Tensor> il{hin};
+    allgather(ol, il)->wait();
+    for (int r = 0; r < ws; ++r) {
+      if (scatter_to) (*scatter_to)[r].copy_(ol[0][r]);
+      else out_flat.narrow(0, r * in.numel(), in.numel()).copy_(ol[0][r].reshape({-1}));
+    }
+    return completed_work(c10d::OpType::ALLGATHER, scatter_to ? *scatter_to : std::vector<at::Tensor>{out_flat}, nullptr);
+  }
+  c10::cuda::CUDAGuard guard(dev);
+  std::vector<at::Tensor> outs = scatter_to ? *scatter_to : std::vector<at::Tensor>{out_flat};
+  CudaPath cp(*this, c10d::OpType::ALLGATHER, "mccl:all_gather", in.nbytes() * ws, outs, dev);
+  at::Tensor flat = out_flat;
+  if (scatter_to) {
+    c10::cuda::CUDAStreamGuard sg(cp.stream);  // temporary belongs to the stream that uses it
+    flat = at::empty({static_cast<int64_t>(ws) * in.numel()}, in.options());
+  }
+  cp.keep(in);
+  cp.keep(flat);
+  const size_t cap = cuda_->arena->parity_bytes() / 256 * 256;
+  const size_t nbytes = in.nbytes();
+  const char* ibase = static_cast<const char*>(in.data_ptr());
+  char* obase = static_cast<char*>(flat.data_ptr());
+  if (nbytes <= cap) {
+    kern::CollParams p = cp.params();
+    p.ctx[0].in = ibase;
+    p.ctx[0].out = obase;
+    p.count = static_cast<int64_t>(nbytes);
+    if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_allgather(p, cp.cfg(nbytes * ws), cp.stream.stream()));
+  } else {
+    // Per-rank blocks larger than the arena: gather slice by slice.  The kernel
+    // places rank r's block at out + r * count, so each slice gathers into a
+    // temporary that is then scattered to its strided destination.
+    c10::cuda::CUDAStreamGuard sg(cp.stream);
+    at::Tensor tmp = at::empty({static_cast<int64_t>(ws * cap)}, in.options().dtype(at::kByte));
+    for (size_t off = 0; off < nbytes; off += cap) {
+      const size_t cnt = std::min(cap, nbytes - off);
+      kern::CollParams p = cp.params();
+      p.ctx[0].in = ibase + off;
+      p.ctx[0].out = tmp.data_ptr();
+      p.count = static_cast<int64_t>(cnt);
+      if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_allgather(p, cp.cfg(cnt * ws), cp.stream.stream()));
+      for (int r = 0; r < ws; ++r)
+        MCCL_CUDA_CHECK(cudaMemcpyAsync(obase + r * nbytes + off, static_cast<char*>(tmp.data_ptr()) + r * cnt, cnt,
+                                        cudaMemcpyDeviceToDevice, cp.stream.stream()));
+    }
+  }
+  if (scatter_to) {
+    c10::cuda::CUDAStreamGuard sg(cp.stream);
+    for (int r = 0; r < ws; ++r) {
+      cp.keep((*scatter_to)[r]);
+      (*scatter_to)[r].reshape({-1}).copy_(flat.narrow(0, r * in.numel(), in.numel()), /*non_blocking=*/true);
+    }
+  }
+  metrics_.record_transport_bytes(nbytes * (ws - 1), nbytes * (ws - 1));
+  return cp.finish();
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_reduce_scatter(at::Tensor& out, const at::Tensor& in_flat,
+                                                                     c10d::ReduceOp::RedOpType op) {
+  const auto dev = out.device().index();
+  ensure_cuda(dev);
+  const int ws = getSize();
+  if (!cuda_->p2p) {
+    at::Tensor hin = in_flat.to(at::kCPU);
+    at::Tensor hout = at::empty({out.numel()}, hin.options());
+    c10d::ReduceScatterOptions o;
+    o.reduceOp = op;
+    _reduce_scatter_base(hout, hin, o)->wait();
+    out.reshape({-1}).copy_(hout);
+    return completed_work(c10d::OpType::REDUCE_SCATTER, {out}, nullptr);
+  }
+  c10::cuda::CUDAGuard guard(dev);
+  const kern::DType dt = to_kern_dtype(out.scalar_type());
+  const size_t esz = out.element_size();
+  const int64_t n = out.numel();
+  CudaPath cp(*this, c10d::OpType::REDUCE_SCATTER, "mccl:reduce_scatter", in_flat.nbytes(), {out}, dev);
+  cp.keep(in_flat);
+  cp.keep(out);
+  const size_t cap = cuda_->arena->parity_bytes();
+  // slot = one chunk slice; ws slots per parity buffer
+  int64_t seg_elems = static_cast<int64_t>((cap / ws) / esz) / 256 * 256;
+  seg_elems = std::max<int64_t>(seg_elems, 256);
+  const char* ibase = static_cast<const char*>(in_flat.data_ptr());
+  char* obase = static_cast<char*>(out.data_ptr());
+  if (n <= seg_elems) {
+    kern::CollParams p = cp.params();
+    p.ctx[0].in = ibase;
+    p.ctx[0].out = obase;
+    p.count = n;
+    p.op = to_kern_op(op);
+    p.scale = op == c10d::ReduceOp::AVG ? 1.0f / ws : 1.0f;
+    if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_reduce_scatter(p, dt, dt, cp.cfg(in_flat.nbytes()), cp.stream.stream()));
+  } else {
+    // Chunks larger than a slot: the kernel wants chunk q at in + q*count, so
+    // pack each slice of all ws chunks contiguously first.
+    c10::cuda::CUDAStreamGuard sg(cp.stream);
+    at::Tensor tmp = at::empty({static_cast<int64_t>(ws) * seg_elems}, out.options());
+    for (int64_t off = 0; off < n; off += seg_elems) {
+      const int64_t cnt = std::min(seg_elems, n - off);
+      for (int r = 0; r < ws; ++r)
+        MCCL_CUDA_CHECK(cudaMemcpyAsync(static_cast<char*>(tmp.data_ptr()) + r * cnt * esz,
+                                        ibase + (static_cast<int64_t>(r) * n + off) * esz, cnt * esz,
+                                        cudaMemcpyDeviceToDevice, cp.stream.stream()));
+      kern::CollParams p = cp.params();
+      p.ctx[0].in = tmp.data_ptr();
+      p.ctx[0].out = obase + off * esz;
+      p.count = cnt;
+      p.op = to_kern_op(op);
+      p.scale = op == c10d::ReduceOp::AVG ? 1.0f / ws : 1.0f;
+      if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_reduce_scatter(p, dt, dt, cp.cfg(cnt * esz * ws), cp.stream.stream()));
+    }
+  }
+  metrics_.record_transport_bytes(out.nbytes() * (ws - 1), out.nbytes() * (ws - 1));
+  return cp.finish();
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_barrier() {
+  const auto dev = cuda_->dev;
+  c10::cuda::CUDAGuard guard(dev);
+  CudaPath cp(*this, c10d::OpType::BARRIER, "mccl:barrier", 0, {}, dev);
+  kern::CollParams p = cp.params();
+  if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_barrier(p, kern::LaunchCfg{}, cp.stream.stream()));
+  return cp.finish(/*blocking=*/true);
+}
+
+// ---------------------------------------------------------------------------
+// Fused top-k compressed allreduce (select -> sparse allgather -> scatter-add
+// with error feedback).  Semantics: standard sparse allgather, identical dense
+// result on every rank (the reference's 2-rank path mixed a decompressed peer
+// with an uncompressed local tensor: reference
+// csrc/backend/ProcessGroupMCCL.cpp:1692-1708; not reproduced).
+// ---------------------------------------------------------------------------
+c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::allreduce_topk(at::Tensor& grad, at::Tensor& residual, double ratio,
+                                                                float scale) {
+  check_alive("allreduce_topk");
+  check_tensor(grad, "allreduce_topk");
+  MCCL_CHECK_TENSOR(grad.is_cuda(), "allreduce_topk: CUDA tensors only");
+  MCCL_CHECK_TENSOR(grad.scalar_type() == at::kFloat || grad.scalar_type() == at::kBFloat16,
+                    "allreduce_topk: float32 or bfloat16 gradients");
+  MCCL_CHECK_TENSOR(residual.is_cuda() && residual.scalar_type() == at::kFloat && residual.is_contiguous() &&
+                        residual.numel() == grad.numel(),
+                    "allreduce_topk: residual must be a float32 CUDA tensor of the gradient's size");
+  MCCL_CHECK_TENSOR(ratio > 0.0 && ratio <= 1.0, "allreduce_topk: ratio must be in (0, 1]");
+  const auto dev = grad.device().index();
+  const int ws = getSize();
+  const int64_t n = grad.numel();
+  MCCL_CHECK_TENSOR(n > 0 && n < (int64_t(1) << 31), "allreduce_topk: element count out of range");
+  int64_t k = std::max<int64_t>(1, static_cast<int64_t>(std::floor(static_cast<double>(n) * ratio)));
+  k = std::min(k, n);
+  const bool bf16 = grad.scalar_type() == at::kBFloat16;
+  c10::cuda::CUDAGuard guard(dev);
+
+  if (ws > 1) ensure_cuda(dev);
+  const bool p2p = ws > 1 && cuda_ && cuda_->p2p;
+  MCCL_CHECK(ws == 1 || p2p, "allreduce_topk needs the NVLink peer data plane (" << data_plane() << ")");
+  const size_t pair_bytes = static_cast<size_t>(k) * 8;
+  if (p2p) MCCL_CHECK(kern::topk_pad(pair_bytes) <= cuda_->arena->parity_bytes(), "top-k payload exceeds the arena");
+
+  // scratch: radix histograms + counters + this rank's (idx,val) list
+  cudaStream_t stream;
+  c10::intrusive_ptr<c10d::Work> result;
+  std::unique_ptr<CudaPath> cp;
+  at::Tensor scratch, pairs;
+  if (p2p) {
+    cp = std::make_unique<CudaPath>(*this, c10d::OpType::ALLREDUCE, "mccl:all_reduce_topk", pair_bytes * ws,
+                                    std::vector<at::Tensor>{grad}, dev);
+    stream = cp->stream.stream();
+    cp->keep(grad);
+    cp->keep(residual);
+  } else {
+    stream = c10::cuda::getCurrentCUDAStream(dev).stream();
+  }
+  {
+    c10::cuda::CUDAStreamGuard sg(p2p ? cp->stream : c10::cuda::getCurrentCUDAStream(dev));
+    scratch = at::empty({static_cast<int64_t>(kern::topk_scratch_bytes())}, grad.options().dtype(at::kByte));
+    pairs = at::empty({k * 2}, grad.options().dtype(at::kInt));
+  }
+  kern::TopkArgs a;
+  a.grad = grad.data_ptr();
+  a.grad_is_bf16 = bf16;
+  a.residual = residual.data_ptr<float>();
+  a.n = n;
+  a.k = k;
+  a.scratch = scratch.data_ptr();
+  a.pairs = pairs.data_ptr();
+  a.scale = scale;
+  if (!(cp && cp->skip)) MCCL_LAUNCH_CHECK(kern::launch_topk_select(a, stream));
+  if (p2p) {
+    kern::CollParams p = cp->params();
+    p.ctx[0].in = pairs.data_ptr();
+    p.ctx[0].out = grad.data_ptr();
+    p.count = k;
+    p.scale = scale;
+    if (!cp->skip) MCCL_LAUNCH_CHECK(kern::launch_topk_exchange_scatter(p, a, cp->cfg(pair_bytes * ws), stream));
+    metrics_.record_transport_bytes(pair_bytes * (ws - 1), pair_bytes * (ws - 1));
+    return cp->finish();
+  }
+  MCCL_LAUNCH_CHECK(kern::launch_topk_local_scatter(a, stream));
+  return completed_work(c10d::OpType::ALLREDUCE, {grad}, nullptr);
+}
+
+}  // namespace mccl

@@ -1,0 +1,110 @@
+// Host-callable launchers of the sm_100a kernels.  This header is plain C++
+// (no ATen, no CUDA headers beyond the runtime API types) so that the backend
+// sources compile with the host compiler and the .cu files compile without
+// pulling in torch.
+#pragma once
+
+#include <cuda_runtime_api.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace mccl {
+namespace kern {
+
+constexpr int kMaxWorld = 8;         // ranks sharing one NVSwitch domain
+constexpr int kMaxCtas = 128;        // upper bound on CTAs of one collective kernel
+constexpr int kNumPhases = 4;        // independent signal arrays per arena
+
+enum DType : int { F32 = 0, F64, F16, BF16, I32, I64, U8, BOOL, DTYPE_COUNT };
+enum RedOp : int { SUM = 0, AVG, MIN, MAX, PRODUCT, REDOP_COUNT };
+
+inline size_t dtype_size(DType t) {
+  switch (t) {
+    case F32: case I32: return 4;
+    case F64: case I64: return 8;
+    case F16: case BF16: return 2;
+    default: return 1;
+  }
+}
+
+// ---- symmetric arena layout -------------------------------------------------
+// Every rank owns one arena:  [ signal pad | data parity 0 | data parity 1 ].
+// The signal pad holds 32-bit epoch flags, all written remotely with release
+// semantics and polled locally with acquire semantics:
+//   entered[src]              src has started collective `seq` (slot-reuse credit)
+//   sig[phase][cta][src]      src's CTA `cta` finished phase `phase` of `seq`
+// Flags only ever grow (the epoch is the process group's arena sequence
+// number), so they are never reset and a late reader can not miss a value.
+constexpr size_t kSignalBytes = 64 * 1024;
+constexpr size_t kEnteredOffset = 0;                         // u32[kMaxWorld]
+constexpr size_t kSigOffset = 256;                           // u32[kNumPhases][kMaxCtas][kMaxWorld]
+static_assert(kSigOffset + size_t(kNumPhases) * kMaxCtas * kMaxWorld * 4 <= kSignalBytes,
+              "signal pad too small");
+
+// Device status block (device memory, one per process group; the host reads it
+// with an asynchronous copy on a side stream).
+// word 0: 0 = healthy, else an ErrorCode; 1: seq; 2: phase; 3: peer waited for.
+enum ErrorCode : uint32_t { ERR_NONE = 0, ERR_WAIT_TIMEOUT = 1, ERR_BOUNDS = 2 };
+constexpr int kStatusWords = 8;
+
+struct RankCtx {
+  int rank;
+  int ws;
+  char* arena[kMaxWorld];  // arena base of every rank as mapped here; arena[rank] is local
+  const void* in;          // this rank's input  (user tensor)
+  void* out;               // this rank's output (user tensor)
+  uint32_t* status;        // kStatusWords words
+};
+
+struct CollParams {
+  RankCtx ctx[kMaxWorld];  // real launch: ctx[0] only (grid.y == 1); emulation: one per rank
+  uint32_t seq;            // arena epoch of this collective (same on every rank)
+  size_t parity_offset;    // byte offset of this epoch's data buffer inside the arena
+  size_t parity_capacity;  // bytes available in it
+  int64_t count;           // elements (meaning depends on the collective)
+  int root;                // broadcast root
+  int op;                  // RedOp
+  float scale;             // multiplied into the result (1/world for AVG, DDP pre-division...)
+  unsigned long long wait_ns;  // bound on every in-kernel wait
+};
+
+struct LaunchCfg {
+  int ctas = 0;     // 0: pick from the message size
+  int threads = 512;
+  int emulate_ranks = 0;  // >0: single-device emulation, grid.y = ranks, cooperative launch
+};
+
+// Picks the CTA count for `bytes` of payload (identical on every rank).
+int pick_ctas(size_t bytes, int ws, int requested);
+
+// Arena-size requirements (bytes of one parity buffer) for a payload.
+size_t oneshot_arena_bytes(size_t nbytes, int ws);
+size_t twoshot_arena_bytes(size_t nbytes, int ws);
+
+// All launchers return cudaSuccess or the launch error; none synchronises.
+// dtype: element type of in/out.  wire: element type stored in the arena
+// (== dtype, or F16/BF16 when dtype is F32: fused wire cast).
+cudaError_t launch_allreduce_oneshot(const CollParams& p, DType dtype, DType wire, LaunchCfg cfg,
+                                     cudaStream_t s);
+cudaError_t launch_allreduce_twoshot(const CollParams& p, DType dtype, DType wire, LaunchCfg cfg,
+                                     cudaStream_t s);
+// ctx.in = ws concatenated chunks of `count` elements, ctx.out = `count` elements.
+cudaError_t launch_reduce_scatter(const CollParams& p, DType dtype, DType wire, LaunchCfg cfg,
+                                  cudaStream_t s);
+// Byte movers: count = bytes per rank.  allgather: out holds ws * count bytes.
+cudaError_t launch_allgather(const CollParams& p, LaunchCfg cfg, cudaStream_t s);
+cudaError_t launch_broadcast(const CollParams& p, LaunchCfg cfg, cudaStream_t s);
+cudaError_t launch_barrier(const CollParams& p, LaunchCfg cfg, cudaStream_t s);
+
+// ---- standalone elementwise kernels (test hooks + local paths) ---------------
+cudaError_t launch_ew_reduce(void* dst, const void* src, int64_t n, DType t, RedOp op, cudaStream_t s);
+cudaError_t launch_ew_scale(void* buf, int64_t n, DType t, double scale, cudaStream_t s);
+cudaError_t launch_ew_accumulate_scale(void* dst, const void* src, int64_t n, DType t, double scale,
+                                       cudaStream_t s);
+// dst(wire dtype) = cast(src(fp32)) and back.
+cudaError_t launch_cast(void* dst, DType dt, const void* src, DType st, int64_t n, float scale,
+                        cudaStream_t s);
+
+}  // namespace kern
+}  // namespace mccl
