@@ -207,6 +207,17 @@ void ProcessGroupMCCL::abort_all_inflight(const std::string& why) {
 c10::intrusive_ptr<WorkMCCL> ProcessGroupMCCL::completed_work(c10d::OpType op, std::vector<at::Tensor> outs,
                                                               const at::Tensor* like) {
   (void)like;
+  // Results on a CUDA device need a CUDA-aware future (a plain future refuses
+  // CUDA tensors): complete it on the caller's current stream, no kernel involved.
+  for (auto& t : outs) {
+    if (t.defined() && t.is_cuda()) {
+      const auto dev = t.device().index();
+      auto w = c10::make_intrusive<WorkMCCL>(getRank(), op, collective_seq_.load(), "mccl:noop", outs,
+                                             /*stream_mode=*/true, dev);
+      w->attach_stream(c10::cuda::getCurrentCUDAStream(dev), false);
+      return w;
+    }
+  }
   auto w = c10::make_intrusive<WorkMCCL>(getRank(), op, collective_seq_.load(), "mccl:noop", std::move(outs),
                                          /*stream_mode=*/false, 0);
   w->mark_complete();

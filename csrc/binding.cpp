@@ -18,6 +18,7 @@
 #include <signal.h>
 #include <unistd.h>
 
+#include <cmath>
 #include <optional>
 
 #include "backend/options.h"
@@ -27,6 +28,8 @@
 #include "compression/compressor.h"
 #include "cpu/reduce.h"
 #include "kernels/api.h"
+#include "kernels/launch_count.h"
+#include "kernels/optim_api.h"
 #include "kernels/topk_api.h"
 #include "runtime/arena.h"
 #include "runtime/engine.h"
@@ -284,6 +287,99 @@ class EmuGroup {
   int ws_;
   unsigned long long wait_ns_;
   std::unique_ptr<SymmetricArena> arena_;
+};
+
+// Device-resident launch plan of the fused multi-tensor AdamW kernel.
+class AdamWPlan {
+ public:
+  AdamWPlan(std::vector<at::Tensor> params, std::vector<at::Tensor> exp_avg, std::vector<at::Tensor> exp_avg_sq)
+      : params_(std::move(params)), m_(std::move(exp_avg)), v_(std::move(exp_avg_sq)) {
+    MCCL_CHECK_TENSOR(!params_.empty() && params_.size() == m_.size() && params_.size() == v_.size(),
+                      "AdamWPlan: list sizes differ");
+    std::vector<int64_t> ptr_p, ptr_m, ptr_v, sizes;
+    std::vector<int32_t> chunks;
+    for (size_t i = 0; i < params_.size(); ++i) {
+      for (const at::Tensor* t : {&params_[i], &m_[i], &v_[i]}) {
+        MCCL_CHECK_TENSOR(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous(),
+                          "AdamWPlan: float32 contiguous CUDA tensors only");
+        MCCL_CHECK_TENSOR(t->numel() == params_[i].numel() && t->device() == params_[0].device(),
+                          "AdamWPlan: shape/device mismatch");
+      }
+      ptr_p.push_back(reinterpret_cast<int64_t>(params_[i].data_ptr()));
+      ptr_m.push_back(reinterpret_cast<int64_t>(m_[i].data_ptr()));
+      ptr_v.push_back(reinterpret_cast<int64_t>(v_[i].data_ptr()));
+      const int64_t n = params_[i].numel();
+      sizes.push_back(n);
+      for (int64_t c = 0; c * kern::kAdamWChunk < n; ++c) {
+        chunks.push_back(static_cast<int32_t>(i));
+        chunks.push_back(static_cast<int32_t>(c));
+      }
+    }
+    auto dev = params_[0].device();
+    auto up64 = [&](const std::vector<int64_t>& v) {
+      return at::tensor(v, at::TensorOptions().dtype(at::kLong)).to(dev);
+    };
+    d_p_ = up64(ptr_p);
+    d_m_ = up64(ptr_m);
+    d_v_ = up64(ptr_v);
+    d_sizes_ = up64(sizes);
+    d_chunks_ = at::tensor(chunks, at::TensorOptions().dtype(at::kInt)).to(dev);
+    num_chunks_ = static_cast<int>(chunks.size() / 2);
+    grad_ptrs_.assign(params_.size(), 0);
+    d_g_ = at::zeros({static_cast<int64_t>(params_.size())}, at::TensorOptions().dtype(at::kLong).device(dev));
+  }
+
+  // grads[i] may move between steps (zero_grad(set_to_none=True)); the pointer
+  // table is re-uploaded only when an address changed.
+  void step(const std::vector<at::Tensor>& grads, double lr, double beta1, double beta2, double eps,
+            double weight_decay, int64_t step, double grad_scale) {
+    MCCL_CHECK_TENSOR(grads.size() == params_.size(), "AdamWPlan.step: expected one gradient per parameter");
+    bool changed = false;
+    for (size_t i = 0; i < grads.size(); ++i) {
+      const at::Tensor& g = grads[i];
+      MCCL_CHECK_TENSOR(g.is_cuda() && g.scalar_type() == at::kFloat && g.is_contiguous() &&
+                            g.numel() == params_[i].numel(),
+                        "AdamWPlan.step: gradient " << i << " must be a float32 contiguous CUDA tensor of the parameter's size");
+      int64_t a = reinterpret_cast<int64_t>(g.data_ptr());
+      if (a != grad_ptrs_[i]) {
+        grad_ptrs_[i] = a;
+        changed = true;
+      }
+    }
+    c10::cuda::CUDAGuard guard(params_[0].device());
+    auto stream = at::cuda::getCurrentCUDAStream();
+    if (changed) {
+      at::Tensor host = at::tensor(grad_ptrs_, at::TensorOptions().dtype(at::kLong));
+      d_g_.copy_(host);
+    }
+    kern::AdamWTable tab;
+    tab.params = reinterpret_cast<const uint64_t*>(d_p_.data_ptr<int64_t>());
+    tab.grads = reinterpret_cast<const uint64_t*>(d_g_.data_ptr<int64_t>());
+    tab.exp_avg = reinterpret_cast<const uint64_t*>(d_m_.data_ptr<int64_t>());
+    tab.exp_avg_sq = reinterpret_cast<const uint64_t*>(d_v_.data_ptr<int64_t>());
+    tab.sizes = d_sizes_.data_ptr<int64_t>();
+    tab.chunks = reinterpret_cast<const int2*>(d_chunks_.data_ptr<int32_t>());
+    tab.num_chunks = num_chunks_;
+    kern::AdamWHyper h;
+    h.lr = static_cast<float>(lr);
+    h.beta1 = static_cast<float>(beta1);
+    h.beta2 = static_cast<float>(beta2);
+    h.eps = static_cast<float>(eps);
+    h.weight_decay = static_cast<float>(weight_decay);
+    const double bc1 = 1.0 - std::pow(beta1, static_cast<double>(step));
+    const double bc2 = 1.0 - std::pow(beta2, static_cast<double>(step));
+    h.step_size = static_cast<float>(lr / bc1);
+    h.inv_sqrt_bias2 = static_cast<float>(1.0 / std::sqrt(bc2));
+    h.grad_scale = static_cast<float>(grad_scale);
+    CK(kern::launch_adamw_multi(tab, h, stream));
+  }
+  int num_chunks() const { return num_chunks_; }
+
+ private:
+  std::vector<at::Tensor> params_, m_, v_;
+  std::vector<int64_t> grad_ptrs_;
+  at::Tensor d_p_, d_g_, d_m_, d_v_, d_sizes_, d_chunks_;
+  int num_chunks_ = 0;
 };
 
 // (pairs as int32 [k,2], k) of the exact top-k of |grad + residual|; residual updated.
@@ -554,6 +650,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            })
       .def("residual_buffers", &TopKCompressor::residual_buffers)
       .def("reset_error_feedback", [](TopKCompressor& c) { c.reset_error_feedback(); });
+
+  // ---- fused optimizer -------------------------------------------------------------------
+  py::class_<AdamWPlan>(m, "AdamWPlan")
+      .def(py::init<std::vector<at::Tensor>, std::vector<at::Tensor>, std::vector<at::Tensor>>(), py::arg("params"),
+           py::arg("exp_avg"), py::arg("exp_avg_sq"))
+      .def("step", &AdamWPlan::step, py::arg("grads"), py::arg("lr"), py::arg("beta1"), py::arg("beta2"),
+           py::arg("eps"), py::arg("weight_decay"), py::arg("step"), py::arg("grad_scale") = 1.0)
+      .def_property_readonly("num_chunks", &AdamWPlan::num_chunks);
+  m.def("_kernel_launches", []() { return kern::launch_counter().load(); });
 
   // ---- top-k kernels ------------------------------------------------------------------------
   m.def("_topk_select", &topk_select, py::arg("grad"), py::arg("residual"), py::arg("ratio"));

@@ -27,6 +27,7 @@
 
 #include "kernels/api.h"
 #include "kernels/flags.cuh"
+#include "kernels/launch_count.h"
 #include "kernels/vec.cuh"
 
 namespace mccl {
@@ -566,6 +567,7 @@ __global__ void __launch_bounds__(128) barrier_kernel(const __grid_constant__ Co
 template <typename K>
 cudaError_t do_launch(K kernel, const CollParams& p, int ctas, int threads, int emulate_ranks,
                       cudaStream_t s) {
+  note_launch();
   if (emulate_ranks > 0) {
     void* args[] = {const_cast<CollParams*>(&p)};
     return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3(ctas, emulate_ranks),

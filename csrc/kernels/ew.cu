@@ -11,6 +11,7 @@
 #include <type_traits>
 
 #include "kernels/api.h"
+#include "kernels/launch_count.h"
 #include "kernels/vec.cuh"
 
 namespace mccl {
@@ -132,6 +133,7 @@ cudaError_t reduce_dispatch_op(T* d, const T* s, int64_t n, RedOp op, cudaStream
 
 cudaError_t launch_ew_reduce(void* dst, const void* src, int64_t n, DType t, RedOp op, cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
+  note_launch();
   switch (t) {
     case F32: return reduce_dispatch_op((float*)dst, (const float*)src, n, op, s);
     case F64: return reduce_dispatch_op((double*)dst, (const double*)src, n, op, s);
@@ -147,6 +149,7 @@ cudaError_t launch_ew_reduce(void* dst, const void* src, int64_t n, DType t, Red
 
 cudaError_t launch_ew_scale(void* buf, int64_t n, DType t, double scale, cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
+  note_launch();
   float f = static_cast<float>(scale);
   switch (t) {
     case F32: ew_scale_kernel<float><<<grid_for((n + 3) / 4, 256), 256, 0, s>>>((float*)buf, n, f); break;
@@ -166,6 +169,7 @@ cudaError_t launch_ew_scale(void* buf, int64_t n, DType t, double scale, cudaStr
 cudaError_t launch_ew_accumulate_scale(void* dst, const void* src, int64_t n, DType t, double scale,
                                        cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
+  note_launch();
   float f = static_cast<float>(scale);
   switch (t) {
     case F32:
@@ -186,6 +190,7 @@ cudaError_t launch_ew_accumulate_scale(void* dst, const void* src, int64_t n, DT
 cudaError_t launch_cast(void* dst, DType dt, const void* src, DType st, int64_t n, float scale,
                         cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
+  note_launch();
   int g = grid_for((n + 3) / 4, 256);
   if (dt == F16 && st == F32) cast_kernel<__half, float><<<g, 256, 0, s>>>((__half*)dst, (const float*)src, n, scale);
   else if (dt == BF16 && st == F32)

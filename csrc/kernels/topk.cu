@@ -11,6 +11,7 @@
 
 #include "kernels/api.h"
 #include "kernels/flags.cuh"
+#include "kernels/launch_count.h"
 #include "kernels/topk_api.h"
 
 namespace mccl {
@@ -368,6 +369,7 @@ size_t topk_scratch_bytes() { return sizeof(TopkScratch); }
 cudaError_t launch_topk_select(const TopkArgs& a, cudaStream_t s) {
   if (a.n <= 0 || a.k <= 0 || a.k > a.n) return cudaErrorInvalidValue;
   TopkScratch* sc = static_cast<TopkScratch*>(a.scratch);
+  note_launch(10);
   const int grid = static_cast<int>(std::min<int64_t>((a.n + 4095) / 4096, 148 * 4));
   topk_clear_kernel<<<8, 256, 0, s>>>(sc);
   if (a.grad_is_bf16)
@@ -388,6 +390,7 @@ cudaError_t launch_topk_select(const TopkArgs& a, cudaStream_t s) {
 }
 
 cudaError_t launch_topk_exchange_scatter(const CollParams& p, const TopkArgs& a, LaunchCfg cfg, cudaStream_t s) {
+  note_launch();
   int ctas = cfg.ctas > 0 ? cfg.ctas : 32;
   if (ctas > 64) ctas = 64;            // ctas * ws flags are polled by one CTA
   if (cfg.emulate_ranks > 0 && ctas > 16) ctas = 16;
@@ -410,6 +413,7 @@ cudaError_t launch_topk_exchange_scatter(const CollParams& p, const TopkArgs& a,
 }
 
 cudaError_t launch_topk_local_scatter(const TopkArgs& a, cudaStream_t s) {
+  note_launch();
   int ctas = static_cast<int>(std::min<int64_t>(148, (a.n + 4095) / 4096));
   if (ctas < 1) ctas = 1;
   if (a.grad_is_bf16)

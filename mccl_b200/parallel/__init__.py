@@ -1,0 +1,4 @@
+"""Data-parallel integration: DDP communication hooks and helpers."""
+from .ddp import fused_avg_hook, topk_hook, TopKState, wrap_ddp
+
+__all__ = ["fused_avg_hook", "topk_hook", "TopKState", "wrap_ddp"]

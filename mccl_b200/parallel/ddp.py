@@ -1,0 +1,100 @@
+"""DistributedDataParallel integration.
+
+Stock ``DistributedDataParallel`` works over the backend unchanged (it issues
+one SUM allreduce per gradient bucket after dividing the bucket by the world
+size in a separate elementwise pass).  The hooks here remove that extra pass:
+
+* :func:`fused_avg_hook` -- the bucket is reduced by ONE kernel that also
+  applies the 1/world scale (and, with ``MCCL_WIRE_DTYPE``, the fp32<->bf16
+  wire cast) in its epilogue.
+* :func:`topk_hook` -- fused top-k compressed allreduce with error feedback
+  (select -> sparse exchange over NVLink -> deterministic scatter-add); the
+  residual lives in a per-bucket fp32 buffer keyed by the bucket index.
+
+Both return futures that are ordered on the communication stream, so no host
+synchronisation happens between backward and the optimizer step.
+"""
+import os
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+from torch.nn.parallel import DistributedDataParallel
+
+
+def _backend_for(process_group, device):
+    pg = process_group if process_group is not None else dist.distributed_c10d._get_default_group()
+    return pg._get_backend(device)
+
+
+def fused_avg_hook(process_group, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
+    """DDP comm hook: ``bucket = sum_over_ranks(bucket) / world`` in one fused kernel."""
+    buf = bucket.buffer()
+    backend = _backend_for(process_group, buf.device)
+    world = backend.size()
+    work = backend.allreduce_scaled(buf, 1.0 / world)
+    return work.get_future().then(lambda f: f.value()[0])
+
+
+class TopKState:
+    """Per-model state of :func:`topk_hook`: ratio and one fp32 residual per bucket."""
+
+    def __init__(self, process_group=None, ratio: Optional[float] = None, warmup_dense_steps: int = 0):
+        self.process_group = process_group
+        self.ratio = float(ratio if ratio is not None else os.environ.get("MCCL_TOPK_RATIO", "0.01"))
+        if not (0.0 < self.ratio <= 1.0):
+            raise ValueError("ratio must be in (0, 1]")
+        self.residuals: Dict[int, torch.Tensor] = {}
+        self.warmup_dense_steps = warmup_dense_steps
+        self.calls = 0
+
+    def residual_for(self, bucket: dist.GradBucket) -> torch.Tensor:
+        buf = bucket.buffer()
+        idx = bucket.index()
+        r = self.residuals.get(idx)
+        if r is None or r.numel() != buf.numel() or r.device != buf.device:
+            r = torch.zeros(buf.numel(), dtype=torch.float32, device=buf.device)
+            self.residuals[idx] = r
+        return r
+
+    def reset(self) -> None:
+        """Drops all residuals (they also restart at zero after a checkpoint resume)."""
+        self.residuals.clear()
+
+
+def topk_hook(state: TopKState, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
+    """DDP comm hook: top-k compressed gradient averaging with error feedback."""
+    buf = bucket.buffer()
+    backend = _backend_for(state.process_group, buf.device)
+    world = backend.size()
+    if bucket.index() == 0:
+        state.calls += 1
+    if state.calls <= state.warmup_dense_steps:
+        work = backend.allreduce_scaled(buf, 1.0 / world)
+    else:
+        work = backend.allreduce_topk(buf, state.residual_for(bucket), state.ratio, 1.0 / world)
+    return work.get_future().then(lambda f: f.value()[0])
+
+
+def wrap_ddp(module: torch.nn.Module, *, device_ids=None, bucket_cap_mb: Optional[int] = None,
+             compression: Optional[str] = None, fused_average: bool = True, process_group=None,
+             **ddp_kwargs) -> DistributedDataParallel:
+    """``DistributedDataParallel`` with the backend's fused hooks installed.
+
+    ``compression`` (default: ``MCCL_COMPRESSION``) selects ``"topk"`` for the
+    compressed hook; otherwise, on CUDA, the fused-average hook replaces DDP's
+    separate divide pass.  ``bucket_cap_mb`` defaults to ``DDP_BUCKET_MB`` or 25.
+    """
+    if bucket_cap_mb is None:
+        bucket_cap_mb = int(os.environ.get("DDP_BUCKET_MB", "25"))
+    ddp_kwargs.setdefault("gradient_as_bucket_view", True)
+    ddp = DistributedDataParallel(module, device_ids=device_ids, bucket_cap_mb=bucket_cap_mb,
+                                  process_group=process_group, **ddp_kwargs)
+    on_cuda = next(module.parameters()).is_cuda
+    mode = compression if compression is not None else os.environ.get("MCCL_COMPRESSION", "none")
+    if on_cuda and mode == "topk":
+        ddp._mccl_topk_state = TopKState(process_group)
+        ddp.register_comm_hook(ddp._mccl_topk_state, topk_hook)
+    elif on_cuda and fused_average:
+        ddp.register_comm_hook(process_group, fused_avg_hook)
+    return ddp

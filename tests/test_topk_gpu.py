@@ -1,0 +1,75 @@
+"""Top-k compression kernels vs the host TopKCompressor (the oracle)."""
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _oracle_pairs(native, adjusted_source, ratio, stable_id=0, comp=None):
+    comp = comp or native.TopKCompressor(ratio)
+    blob = comp.compress(adjusted_source.cpu().float().contiguous(), stable_id)
+    k = struct.unpack_from("<I", blob, 0)[0]
+    rec = np.frombuffer(blob, dtype=np.dtype([("i", "<u4"), ("v", "<f4")]), offset=4, count=k)
+    return comp, rec["i"].astype(np.int64).tolist(), rec["v"].tolist()
+
+
+@pytest.mark.parametrize("n,ratio", [(10, 0.5), (1000, 0.01), (65537, 0.1), (1_000_003, 0.01), (300_001, 1.0)])
+def test_select_matches_host_oracle(native, cuda_device, n, ratio):
+    g = torch.randn(n)
+    comp, idx, val = _oracle_pairs(native, g, ratio)
+    res = torch.zeros(n, device=cuda_device)
+    pairs = native._topk_select(g.to(cuda_device), res, ratio)
+    torch.cuda.synchronize()
+    got_idx = pairs[:, 0].cpu().tolist()
+    got_val = pairs[:, 1].cpu().view(torch.float32).tolist()
+    assert got_idx == idx
+    assert got_val == val
+    assert torch.equal(res.cpu(), comp.residual(0))
+
+
+def test_select_ties_take_lower_index(native, cuda_device):
+    g = torch.tensor([1.0, -2.0, 2.0, 2.0, -2.0, 0.5, 2.0, 3.0])
+    res = torch.zeros(8, device=cuda_device)
+    pairs = native._topk_select(g.to(cuda_device), res, 0.5)  # k = 4: 3.0 and three of the |2.0|
+    assert pairs[:, 0].cpu().tolist() == [1, 2, 3, 7]
+    assert res.cpu().tolist() == [1.0, 0.0, 0.0, 0.0, -2.0, 0.5, 2.0, 0.0]
+
+
+def test_error_feedback_accumulates_like_oracle(native, cuda_device):
+    n, ratio = 50_000, 0.02
+    comp = native.TopKCompressor(ratio)
+    res = torch.zeros(n, device=cuda_device)
+    for step in range(5):
+        g = torch.randn(n, generator=torch.Generator().manual_seed(step))
+        _, idx, val = _oracle_pairs(native, g, ratio, comp=comp)
+        pairs = native._topk_select(g.to(cuda_device), res, ratio)
+        assert pairs[:, 0].cpu().tolist() == idx, f"step {step}"
+        assert torch.equal(res.cpu(), comp.residual(0))
+
+
+@pytest.mark.parametrize("ws", [2, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_topk_allreduce_is_consistent(native, cuda_device, ws, dtype):
+    n, ratio = 200_003, 0.01
+    grp = native.EmuGroup(ws, 8 << 20)
+    grads = [torch.randn(n, generator=torch.Generator().manual_seed(r)).to(dtype).to(cuda_device) for r in range(ws)]
+    orig = [g.clone() for g in grads]
+    residuals = [torch.zeros(n, device=cuda_device) for _ in range(ws)]
+    grp.topk_allreduce(grads, residuals, ratio, 1.0 / ws)
+    torch.cuda.synchronize()
+    for r in range(1, ws):
+        assert torch.equal(grads[0], grads[r]), "dense results differ across ranks"
+    # dense reference: sum over ranks (in rank order) of each rank's sparse selection, scaled
+    dense = torch.zeros(n, dtype=torch.float32)
+    scale = torch.tensor(1.0 / ws, dtype=torch.float32)
+    for r in range(ws):
+        comp, idx, val = _oracle_pairs(native, orig[r].float(), ratio)
+        if dtype == torch.float32:
+            dense[idx] += torch.tensor(val) * scale
+        else:
+            dense[idx] = (dense[idx].to(dtype).float() + torch.tensor(val) * scale).to(dtype).float()
+        assert torch.equal(residuals[r].cpu(), comp.residual(0))
+    assert torch.equal(grads[0].float().cpu(), dense.to(dtype).float())
