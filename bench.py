@@ -37,7 +37,7 @@ IN_FEATURES, CLASSES = 2048, 1000
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="mccl", choices=["mccl", "nccl", "reference"])
     ap.add_argument("--bucket-mb", type=int, default=25)
@@ -49,7 +49,7 @@ def parse_args():
 class ClockSampler(threading.Thread):
     """Samples SM clocks and throttle reasons of one GPU through NVML while a region is timed."""
 
-    def __init__(self, index: int, period_s: float = 0.05):
+    def __init__(self, index: int, period_s: float = 0.02):
         super().__init__(daemon=True)
         self.index, self.period = index, period_s
         self.samples, self.reasons, self.max_mhz = [], set(), None

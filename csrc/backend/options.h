@@ -60,6 +60,7 @@ struct MCCLOptions : c10d::Backend::Options {
   std::string algo = "auto";            // auto | oneshot | twoshot | staged
   int64_t oneshot_max_bytes = -1;       // -1: tuner table
   int64_t comm_ctas = 0;                // 0: from message size
+  int64_t tiles = 1;                    // two-shot pipeline tiles per CTA (1: bulk phases)
   int64_t arena_bytes = 128ll << 20;    // one parity buffer
   int64_t device_wait_us = 60ll * 1000 * 1000;
   bool blocking_wait = false;
@@ -85,6 +86,7 @@ struct MCCLOptions : c10d::Backend::Options {
     o->algo = env_str("MCCL_ALGO", "auto");
     o->oneshot_max_bytes = env_int("MCCL_ONESHOT_MAX_BYTES", -1);
     o->comm_ctas = env_int("MCCL_COMM_CTAS", 0);
+    o->tiles = env_int("MCCL_TILES", 1);
     o->arena_bytes = env_int("MCCL_ARENA_BYTES", 128ll << 20);
     int64_t wd_us = o->watchdog_timeout.count() * 1000;
     o->device_wait_us = env_int("MCCL_DEVICE_WAIT_US", std::min<int64_t>(60ll * 1000 * 1000, wd_us));

@@ -113,6 +113,8 @@ class ProcessGroupMCCL : public c10d::Backend {
   // Test hook: next CUDA collective is skipped on this rank (peers must time out).
   void test_skip_next_launch() { skip_next_launch_.store(true); }
   Tuner& tuner() { return tuner_; }
+  // globaltimer stamps (ns) of the last arena collective's phases; needs MCCL_PHASE_STAMPS=1.
+  std::vector<int64_t> last_phase_stamps();
 
  private:
   friend struct CudaPath;

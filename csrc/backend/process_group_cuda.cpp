@@ -125,7 +125,20 @@ void ProcessGroupMCCL::ensure_cuda(c10::DeviceIndex dev) {
     MCCL_INFO("rank %d: NVLink peer arena mapped on %d ranks (%lld MiB x2 per rank)", getRank(), ws,
               (long long)(options_->arena_bytes >> 20));
   }
+  if (st->arena && env_bool("MCCL_PHASE_STAMPS", false)) st->arena->enable_stamps(true);
   cuda_ = std::move(st);
+}
+
+std::vector<int64_t> ProcessGroupMCCL::last_phase_stamps() {
+  std::vector<int64_t> out;
+  std::lock_guard<std::mutex> g(cuda_mu_);
+  if (!cuda_ || !cuda_->arena) return out;
+  c10::cuda::CUDAGuard guard(cuda_->dev);
+  MCCL_CUDA_CHECK(cudaStreamSynchronize(cuda_->comm->stream()));
+  unsigned long long st[kern::kStampSlots];
+  cuda_->arena->read_stamps(st, cuda_->poll_stream);
+  for (auto v : st) out.push_back(static_cast<int64_t>(v));
+  return out;
 }
 
 void ProcessGroupMCCL::poll_device() {
@@ -226,7 +239,6 @@ struct CudaPath {
   CudaPath(ProcessGroupMCCL& pg_, c10d::OpType op, const char* name, uint64_t bytes, std::vector<at::Tensor> outs,
            c10::DeviceIndex dev)
       : pg(pg_), cs(*pg_.cuda_), seq(pg_.next_seq()), stream(c10::cuda::getCurrentCUDAStream(dev)) {
-    if (pg.health_) pg.health_->check_now();  // learn about dead peers before launching
     pg.check_alive(name);
     work = c10::make_intrusive<WorkMCCL>(pg.getRank(), op, seq, name, std::move(outs), /*stream_mode=*/true, dev);
     pg.metrics_.op_start(seq, name, bytes);
@@ -252,6 +264,7 @@ struct CudaPath {
     cs.arena->fill_params(p, cs.arena->next_epoch());
     p.scale = 1.0f;
     p.wait_ns = static_cast<unsigned long long>(pg.options_->device_wait_us) * 1000ull;
+    p.tiles = static_cast<int>(pg.options_->tiles);
     return p;
   }
 
@@ -342,7 +355,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allreduce(at::Tensor& t, c
     p.scale = (op == c10d::ReduceOp::AVG ? 1.0f / ws : 1.0f) * prescale;
     if (!cp.skip) {
       if (v == Variant::ONESHOT)
-        MCCL_LAUNCH_CHECK(kern::launch_allreduce_oneshot(p, dt, wire, cp.cfg(wire_bytes), cp.stream.stream()));
+        MCCL_LAUNCH_CHECK(kern::launch_allreduce_oneshot(p, dt, wire, cp.cfg(wire_bytes * (ws - 1)), cp.stream.stream()));
       else
         MCCL_LAUNCH_CHECK(kern::launch_allreduce_twoshot(p, dt, wire, cp.cfg(wire_bytes), cp.stream.stream()));
     }

@@ -510,6 +510,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              return pg.allreduce_scaled(v, static_cast<float>(scale));
            },
            py::arg("tensor"), py::arg("scale"), py::call_guard<py::gil_scoped_release>())
+      .def("last_phase_stamps", &ProcessGroupMCCL::last_phase_stamps, py::call_guard<py::gil_scoped_release>())
       .def("_test_skip_next_launch", &ProcessGroupMCCL::test_skip_next_launch)
       .def("shutdown", &ProcessGroupMCCL::shutdown, py::call_guard<py::gil_scoped_release>());
 

@@ -47,6 +47,10 @@ static_assert(kSigOffset + size_t(kNumPhases) * kMaxCtas * kMaxWorld * 4 <= kSig
 // word 0: 0 = healthy, else an ErrorCode; 1: seq; 2: phase; 3: peer waited for.
 enum ErrorCode : uint32_t { ERR_NONE = 0, ERR_WAIT_TIMEOUT = 1, ERR_BOUNDS = 2 };
 constexpr int kStatusWords = 8;
+// Phase stamps (ns, %globaltimer) of the last collective, written by CTA 0:
+// 0 kernel start, 1 entered, 2 push done, 3 peers' pushes seen, 4 reduce done,
+// 5 peers' reduces seen, 6 pull done / end.
+constexpr int kStampSlots = 8;
 
 struct RankCtx {
   int rank;
@@ -55,6 +59,7 @@ struct RankCtx {
   const void* in;          // this rank's input  (user tensor)
   void* out;               // this rank's output (user tensor)
   uint32_t* status;        // kStatusWords words
+  unsigned long long* stamps;  // optional: kStampSlots globaltimer stamps written by CTA 0 (nullptr = off)
 };
 
 struct CollParams {
@@ -67,6 +72,7 @@ struct CollParams {
   int op;                  // RedOp
   float scale;             // multiplied into the result (1/world for AVG, DDP pre-division...)
   unsigned long long wait_ns;  // bound on every in-kernel wait
+  int tiles;               // two-shot: pipeline tiles per CTA (<=1: bulk phases)
 };
 
 struct LaunchCfg {

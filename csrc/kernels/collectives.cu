@@ -131,12 +131,12 @@ __device__ __forceinline__ bool enter_collective(const CtaCtx& k) {
 }
 
 // Publishes "my CTA finished `phase`" to every rank (self included).
-__device__ __forceinline__ void signal_all(const CtaCtx& k, int phase) {
+__device__ __forceinline__ void signal_all(const CtaCtx& k, int phase, uint32_t count = kSigDone) {
   const RankCtx& c = *k.c;
   __syncthreads();
   if (k.tid < c.ws) {
     fence_sys();
-    st_release_sys(sig_flag(c.arena[k.tid], phase, k.cta, c.rank), k.p->seq);
+    st_release_sys(sig_flag(c.arena[k.tid], phase, k.cta, c.rank), sig_value(k.p->seq, count));
   }
 }
 __device__ __forceinline__ void signal_one(const CtaCtx& k, int phase, int dst) {
@@ -144,17 +144,21 @@ __device__ __forceinline__ void signal_one(const CtaCtx& k, int phase, int dst) 
   __syncthreads();
   if (k.tid == 0) {
     fence_sys();
-    st_release_sys(sig_flag(c.arena[dst], phase, k.cta, c.rank), k.p->seq);
+    st_release_sys(sig_flag(c.arena[dst], phase, k.cta, c.rank), sig_value(k.p->seq, kSigDone));
   }
 }
 // Waits for the same CTA index of every rank (or of `only`, if >= 0).
-__device__ __forceinline__ bool wait_all(const CtaCtx& k, int phase, int only = -1) {
+__device__ __forceinline__ bool wait_all(const CtaCtx& k, int phase, int only = -1, uint32_t count = kSigDone) {
   const RankCtx& c = *k.c;
   bool ok = true;
   if (k.tid < c.ws && (only < 0 || k.tid == only))
-    ok = wait_epoch(sig_flag(c.arena[c.rank], phase, k.cta, k.tid), k.p->seq, k.p->wait_ns, c.status,
+    ok = wait_epoch(sig_flag(c.arena[c.rank], phase, k.cta, k.tid), sig_value(k.p->seq, count), k.p->wait_ns, c.status,
                     static_cast<uint32_t>(phase), static_cast<uint32_t>(k.tid));
   return __syncthreads_and(ok ? 1 : 0) != 0;
+}
+
+__device__ __forceinline__ void stamp(const CtaCtx& k, int slot) {
+  if (k.c->stamps != nullptr && k.cta == 0 && k.tid == 0) k.c->stamps[slot] = globaltimer_ns();
 }
 
 __device__ __forceinline__ CtaCtx make_ctx(const CollParams& p) {
@@ -169,10 +173,11 @@ __device__ __forceinline__ CtaCtx make_ctx(const CollParams& p) {
 }
 
 template <typename T, int OP>
-__device__ __forceinline__ void combine(typename Traits<T>::Acc* acc, const typename Traits<T>::Acc* x, int n) {
+__device__ __forceinline__ void combine(typename Traits<T>::Acc* acc, const typename Traits<T>::Acc* x, int n,
+                                        int rt_op = 0) {
 #pragma unroll
   for (int j = 0; j < 16; ++j)
-    if (j < n) acc[j] = Reduce<T, OP>::apply(acc[j], x[j]);
+    if (j < n) acc[j] = OP == kRuntimeOp ? Reduce<T, OP>::apply_rt(rt_op, acc[j], x[j]) : Reduce<T, OP>::apply(acc[j], x[j]);
 }
 
 // ---------------------------------------------------------------------------
@@ -283,57 +288,107 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const __grid_con
 //            the owners' arenas straight into its output tensor
 // For reduce_scatter the "chunks" are the ws equal parts of the input list.
 // ---------------------------------------------------------------------------
-template <typename T, typename W, int OP>
-__device__ __forceinline__ void reduce_own_chunk(const CtaCtx& k, const T* in_chunk, int64_t in_n,
-                                                 T* out_chunk, int64_t out_n, int64_t chunk_units,
-                                                 size_t slot_bytes, char* local_buf, bool keep_wire) {
+// Reduces units [u0, u1) of the chunk this rank owns.  G units are in flight per
+// thread so that G * ws independent 16-byte loads are outstanding: with few
+// ranks one unit per thread would leave HBM idle.
+template <typename T, typename W, int OP, int G>
+__device__ __forceinline__ void reduce_tile_g(const CtaCtx& k, const T* in_chunk, int64_t own_n, T* out_chunk,
+                                              int64_t u0, int64_t u1, size_t slot_bytes, char* local_buf,
+                                              bool keep_wire, bool in_al, bool out_al) {
   using U = Unit<T, W>;
   using Acc = typename U::Acc;
   const RankCtx& c = *k.c;
-  const bool in_al = is_aligned16(in_chunk), out_al = is_aligned16(out_chunk);
-  const int64_t stride = static_cast<int64_t>(k.nctas) * k.nthreads;
-  for (int64_t u = static_cast<int64_t>(k.cta) * k.nthreads + k.tid; u < chunk_units; u += stride) {
-    Acc acc[U::N], x[U::N];
-    uint4 raw[kMaxWorld];
+  constexpr int MAXR = kMaxWorld / G;  // ranks this variant supports
+  constexpr int TV = sizeof(T) * U::N / 16;  // 16-byte vectors of T per unit
+  constexpr int PER = 16 / sizeof(T);
+  for (int64_t ub = u0 + k.tid; ub < u1; ub += static_cast<int64_t>(k.nthreads) * G) {
+    uint4 raw[G][MAXR];
+    uint4 own[G][TV];
+    // all loads of the group first (peers' slots and this rank's own input), then the math
 #pragma unroll
-    for (int r = 0; r < kMaxWorld; ++r)
-      if (r < c.ws && r != c.rank) raw[r] = ldg16(local_buf + r * slot_bytes + u * 16);
+    for (int g = 0; g < G; ++g) {
+      const int64_t u = ub + static_cast<int64_t>(g) * k.nthreads;
 #pragma unroll
-    for (int r = 0; r < kMaxWorld; ++r) {
-      if (r >= c.ws) break;
-      if (r == c.rank) {
-        U::load_T(in_chunk, u * U::N, in_n, in_al, x);
-        U::round_through_wire(x);
-      } else {
-        U::unpack_W(raw[r], x);
-      }
-      if (r == 0) {
+      for (int r = 0; r < MAXR; ++r)
+        if (u < u1 && r < c.ws && r != c.rank) raw[g][r] = ldg16(local_buf + r * slot_bytes + u * 16);
+      if (u < u1 && in_al && (u + 1) * U::N <= own_n) {
 #pragma unroll
-        for (int j = 0; j < U::N; ++j) acc[j] = x[j];
-      } else {
-        combine<T, OP>(acc, x, U::N);
+        for (int v = 0; v < TV; ++v) own[g][v] = ldg16(in_chunk + u * U::N + v * PER);
       }
     }
-    if (OP == AVG || k.p->scale != 1.0f) {
 #pragma unroll
-      for (int j = 0; j < U::N; ++j) acc[j] = Traits<T>::scale(acc[j], k.p->scale);
+    for (int g = 0; g < G; ++g) {
+      const int64_t u = ub + static_cast<int64_t>(g) * k.nthreads;
+      if (u >= u1) break;
+      Acc acc[U::N], x[U::N];
+#pragma unroll
+      for (int r = 0; r < MAXR; ++r) {
+        if (r >= c.ws) break;
+        if (r == c.rank) {
+          if (in_al && (u + 1) * U::N <= own_n) {
+#pragma unroll
+            for (int v = 0; v < TV; ++v) {
+              typename VecOf<T>::U uu;
+              uu.raw = own[g][v];
+#pragma unroll
+              for (int j = 0; j < PER; ++j) x[v * PER + j] = Traits<T>::load(uu.e[j]);
+            }
+          } else {
+            U::load_T(in_chunk, u * U::N, own_n, in_al, x);
+          }
+          U::round_through_wire(x);
+        } else {
+          U::unpack_W(raw[g][r], x);
+        }
+        if (r == 0) {
+#pragma unroll
+          for (int j = 0; j < U::N; ++j) acc[j] = x[j];
+        } else {
+          combine<T, OP>(acc, x, U::N, k.p->op);
+        }
+      }
+      if (k.p->op == AVG || k.p->scale != 1.0f) {
+#pragma unroll
+        for (int j = 0; j < U::N; ++j) acc[j] = Traits<T>::scale(acc[j], k.p->scale);
+      }
+      if (keep_wire) {
+        uint4 w = U::pack_W(acc);
+        stg16(local_buf + c.rank * slot_bytes + u * 16, w);
+        U::unpack_W(w, acc);  // the owner outputs exactly what the peers will pull
+      }
+      U::store_T(out_chunk, u * U::N, own_n, out_al, acc);
     }
-    if (keep_wire) {
-      uint4 w = U::pack_W(acc);
-      stg16(local_buf + c.rank * slot_bytes + u * 16, w);
-      U::unpack_W(w, acc);  // the owner outputs exactly what the peers will pull
-    }
-    U::store_T(out_chunk, u * U::N, out_n, out_al, acc);
   }
 }
 
-template <typename T, typename W, bool kAllGather>
+template <typename T, typename W, int OP>
+__device__ __forceinline__ void reduce_tile(const CtaCtx& k, const T* in_chunk, int64_t own_n, T* out_chunk,
+                                            int64_t u0, int64_t u1, size_t slot_bytes, char* local_buf,
+                                            bool keep_wire) {
+  const bool in_al = is_aligned16(in_chunk), out_al = is_aligned16(out_chunk);
+  const int ws = k.c->ws;
+  if (ws <= 4) reduce_tile_g<T, W, OP, 2>(k, in_chunk, own_n, out_chunk, u0, u1, slot_bytes, local_buf, keep_wire, in_al, out_al);
+  else reduce_tile_g<T, W, OP, 1>(k, in_chunk, own_n, out_chunk, u0, u1, slot_bytes, local_buf, keep_wire, in_al, out_al);
+}
+
+// Tile-pipelined two-shot.  A CTA's share of the chunk index space is cut into
+// tiles of nthreads * kTileUnroll 16-byte units; in iteration `it` the CTA
+// pushes tile it, reduces tile it-1 (whose peer pushes were signalled one
+// iteration ago) and pulls tile it-2, so link traffic, the HBM-bound reduction
+// and the flag round trips overlap instead of forming three bulk-synchronous
+// phases.
+constexpr int kTileUnroll = 4;
+
+// kSum: SUM/AVG (AVG differs only by the scale); otherwise MIN/MAX/PRODUCT at run time.
+template <typename T, typename W, bool kAllGather, bool kSum>
 __global__ void __launch_bounds__(512) twoshot_kernel(const __grid_constant__ CollParams p) {
   using U = Unit<T, W>;
   using Acc = typename U::Acc;
   CtaCtx k = make_ctx(p);
   const RankCtx& c = *k.c;
+  stamp(k, 0);
   if (!enter_collective(k)) return;
+  stamp(k, 1);
 
   const T* in = static_cast<const T*>(c.in);
   T* out = static_cast<T*>(c.out);
@@ -350,9 +405,6 @@ __global__ void __launch_bounds__(512) twoshot_kernel(const __grid_constant__ Co
   }
   const int64_t total = kAllGather ? p.count : p.count * c.ws;
   const size_t slot_bytes = round_up(static_cast<size_t>(chunk_units) * 16, 128);
-  const int64_t stride = static_cast<int64_t>(k.nctas) * k.nthreads;
-  const int64_t first = static_cast<int64_t>(k.cta) * k.nthreads + k.tid;
-
   auto chunk_len = [&](int q) -> int64_t {  // valid elements of chunk q
     int64_t b = static_cast<int64_t>(q) * chunk_elems;
     int64_t e = b + chunk_elems;
@@ -360,88 +412,109 @@ __global__ void __launch_bounds__(512) twoshot_kernel(const __grid_constant__ Co
     return e > b ? e - b : 0;
   };
 
-  // ---- phase 0: push my part of every peer's chunk --------------------------
-  for (int d = 1; d < c.ws; ++d) {
-    int q = c.rank + d;
-    if (q >= c.ws) q -= c.ws;
-    const T* src = in + static_cast<int64_t>(q) * chunk_elems;
-    const int64_t src_n = chunk_len(q);
-    const bool al = is_aligned16(src);
-    char* dst = c.arena[q] + p.parity_offset + c.rank * slot_bytes;
-    for (int64_t u0 = first; u0 < chunk_units; u0 += stride * kUnroll) {
-      uint4 v[kUnroll];
+  // A tile is a whole number of batches (nthreads * kTileUnroll units); the
+  // requested tiles per CTA fix its size.  One tile per CTA = bulk phases.
+  const int64_t batch_units = static_cast<int64_t>(k.nthreads) * kTileUnroll;
+  const int64_t want_tiles = p.tiles > 1 ? p.tiles : 1;
+  const int64_t per_cta_units = (chunk_units + k.nctas - 1) / k.nctas;
+  int64_t tile_units = ((per_cta_units + want_tiles - 1) / want_tiles + batch_units - 1) / batch_units * batch_units;
+  if (tile_units < batch_units) tile_units = batch_units;
+  const int64_t ntiles_total = (chunk_units + tile_units - 1) / tile_units;
+  // tiles g = cta, cta + nctas, ... belong to this CTA
+  const int64_t my_tiles = ntiles_total > k.cta ? (ntiles_total - k.cta + k.nctas - 1) / k.nctas : 0;
+  auto tile_begin = [&](int64_t j) { return (static_cast<int64_t>(k.cta) + j * k.nctas) * tile_units; };
+  auto tile_end = [&](int64_t j) {
+    int64_t e = tile_begin(j) + tile_units;
+    return e < chunk_units ? e : chunk_units;
+  };
+  char* local_buf = c.arena[c.rank] + p.parity_offset;
+  const T* in_chunk = in + static_cast<int64_t>(c.rank) * chunk_elems;
+  const int64_t own_n = chunk_len(c.rank);
+  T* out_chunk = kAllGather ? out + static_cast<int64_t>(c.rank) * chunk_elems : out;
+  const int last_stage = kAllGather ? 2 : 1;
+
+  for (int64_t it = 0; it < my_tiles + last_stage; ++it) {
+    // ---- stage 0: push my part of tile `it` of every peer's chunk ------------
+    if (it < my_tiles) {
+      const int64_t u0 = tile_begin(it), u1 = tile_end(it);
+      for (int d = 1; d < c.ws; ++d) {
+        int q = c.rank + d;
+        if (q >= c.ws) q -= c.ws;
+        const T* src = in + static_cast<int64_t>(q) * chunk_elems;
+        const int64_t src_n = chunk_len(q);
+        const bool al = is_aligned16(src);
+        char* dst = c.arena[q] + p.parity_offset + c.rank * slot_bytes;
+        for (int64_t ub = u0; ub < u1; ub += batch_units) {
+          uint4 v[kTileUnroll];
 #pragma unroll
-      for (int i = 0; i < kUnroll; ++i) {
-        int64_t u = u0 + i * stride;
-        if (u < chunk_units) {
-          if (U::kSame && al && (u + 1) * U::N <= src_n) {
-            v[i] = ldg16(src + u * U::N);
-          } else {
-            Acc a[U::N];
-            U::load_T(src, u * U::N, src_n, al, a);
-            v[i] = U::pack_W(a);
+          for (int i = 0; i < kTileUnroll; ++i) {
+            const int64_t u = ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
+            if (u < u1) {
+              if (U::kSame && al && (u + 1) * U::N <= src_n) {
+                v[i] = ldg16(src + u * U::N);
+              } else {
+                Acc a[U::N];
+                U::load_T(src, u * U::N, src_n, al, a);
+                v[i] = U::pack_W(a);
+              }
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < kTileUnroll; ++i) {
+            const int64_t u = ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
+            if (u < u1) stg16(dst + u * 16, v[i]);
           }
         }
       }
-#pragma unroll
-      for (int i = 0; i < kUnroll; ++i) {
-        int64_t u = u0 + i * stride;
-        if (u < chunk_units) stg16(dst + u * 16, v[i]);
-      }
+      if (it == my_tiles - 1) stamp(k, 2);
+      signal_all(k, 0, static_cast<uint32_t>(it + 1));
     }
-  }
-  signal_all(k, 0);
-  if (!wait_all(k, 0)) return;
-
-  // ---- phase 1: reduce the chunk this rank owns ------------------------------
-  {
-    char* local_buf = c.arena[c.rank] + p.parity_offset;
-    const T* in_chunk = in + static_cast<int64_t>(c.rank) * chunk_elems;
-    const int64_t own_n = chunk_len(c.rank);
-    T* out_chunk = kAllGather ? out + static_cast<int64_t>(c.rank) * chunk_elems : out;
-    switch (p.op) {
-      case SUM: reduce_own_chunk<T, W, SUM>(k, in_chunk, own_n, out_chunk, own_n, chunk_units, slot_bytes, local_buf, kAllGather); break;
-      case AVG: reduce_own_chunk<T, W, AVG>(k, in_chunk, own_n, out_chunk, own_n, chunk_units, slot_bytes, local_buf, kAllGather); break;
-      case MIN: reduce_own_chunk<T, W, MIN>(k, in_chunk, own_n, out_chunk, own_n, chunk_units, slot_bytes, local_buf, kAllGather); break;
-      case MAX: reduce_own_chunk<T, W, MAX>(k, in_chunk, own_n, out_chunk, own_n, chunk_units, slot_bytes, local_buf, kAllGather); break;
-      default: reduce_own_chunk<T, W, PRODUCT>(k, in_chunk, own_n, out_chunk, own_n, chunk_units, slot_bytes, local_buf, kAllGather); break;
+    // ---- stage 1: reduce tile it-1 of the chunk this rank owns ---------------
+    if (it >= 1 && it - 1 < my_tiles) {
+      if (!wait_all(k, 0, -1, static_cast<uint32_t>(it))) return;
+      if (it == my_tiles) stamp(k, 3);
+      const int64_t u0 = tile_begin(it - 1), u1 = tile_end(it - 1);
+      reduce_tile<T, W, kSum ? SUM : kRuntimeOp>(k, in_chunk, own_n, out_chunk, u0, u1, slot_bytes, local_buf, kAllGather);
+      if (it == my_tiles) stamp(k, 4);
+      if (kAllGather) signal_all(k, 1, static_cast<uint32_t>(it));
     }
-  }
-  if (!kAllGather) return;
-
-  signal_all(k, 1);
-  if (!wait_all(k, 1)) return;
-
-  // ---- phase 2: pull the reduced chunks from their owners --------------------
-  for (int d = 1; d < c.ws; ++d) {
-    int q = c.rank + d;
-    if (q >= c.ws) q -= c.ws;
-    const char* src = c.arena[q] + p.parity_offset + q * slot_bytes;
-    T* dst = out + static_cast<int64_t>(q) * chunk_elems;
-    const int64_t dst_n = chunk_len(q);
-    const bool al = is_aligned16(dst);
-    for (int64_t u0 = first; u0 < chunk_units; u0 += stride * kUnroll) {
-      uint4 v[kUnroll];
+    // ---- stage 2: pull reduced tile it-2 from its owners ----------------------
+    if (kAllGather && it >= 2 && it - 2 < my_tiles) {
+      if (!wait_all(k, 1, -1, static_cast<uint32_t>(it - 1))) return;
+      if (it == my_tiles + 1) stamp(k, 5);
+      const int64_t u0 = tile_begin(it - 2), u1 = tile_end(it - 2);
+      for (int d = 1; d < c.ws; ++d) {
+        int q = c.rank + d;
+        if (q >= c.ws) q -= c.ws;
+        const char* src = c.arena[q] + p.parity_offset + q * slot_bytes;
+        T* dst = out + static_cast<int64_t>(q) * chunk_elems;
+        const int64_t dst_n = chunk_len(q);
+        const bool al = is_aligned16(dst);
+        for (int64_t ub = u0; ub < u1; ub += batch_units) {
+          uint4 v[kTileUnroll];
 #pragma unroll
-      for (int i = 0; i < kUnroll; ++i) {
-        int64_t u = u0 + i * stride;
-        if (u < chunk_units) v[i] = ldg16(src + u * 16);
-      }
+          for (int i = 0; i < kTileUnroll; ++i) {
+            const int64_t u = ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
+            if (u < u1) v[i] = ldg16(src + u * 16);
+          }
 #pragma unroll
-      for (int i = 0; i < kUnroll; ++i) {
-        int64_t u = u0 + i * stride;
-        if (u < chunk_units && u * U::N < dst_n) {
-          if (U::kSame && al && (u + 1) * U::N <= dst_n) {
-            stg16(dst + u * U::N, v[i]);
-          } else {
-            Acc a[U::N];
-            U::unpack_W(v[i], a);
-            U::store_T(dst, u * U::N, dst_n, al, a);
+          for (int i = 0; i < kTileUnroll; ++i) {
+            const int64_t u = ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
+            if (u < u1 && u * U::N < dst_n) {
+              if (U::kSame && al && (u + 1) * U::N <= dst_n) {
+                stg16(dst + u * U::N, v[i]);
+              } else {
+                Acc a[U::N];
+                U::unpack_W(v[i], a);
+                U::store_T(dst, u * U::N, dst_n, al, a);
+              }
+            }
           }
         }
       }
     }
   }
+  stamp(k, 6);
 }
 
 // ---------------------------------------------------------------------------
@@ -603,12 +676,18 @@ template <typename T, typename W> struct OneShotL {
 };
 template <typename T, typename W> struct TwoShotL {
   static cudaError_t go(const CollParams& p, int ctas, const LaunchCfg& cfg, cudaStream_t s) {
-    return do_launch(twoshot_kernel<T, W, true>, p, ctas, cfg.threads, cfg.emulate_ranks, s);
+    if (p.op == SUM || p.op == AVG)
+      return do_launch(twoshot_kernel<T, W, true, true>, p, ctas, cfg.threads, cfg.emulate_ranks, s);
+    if (!std::is_same<T, W>::value) return cudaErrorInvalidValue;  // wire cast is defined for sums only
+    return do_launch(twoshot_kernel<T, T, true, false>, p, ctas, cfg.threads, cfg.emulate_ranks, s);
   }
 };
 template <typename T, typename W> struct ReduceScatterL {
   static cudaError_t go(const CollParams& p, int ctas, const LaunchCfg& cfg, cudaStream_t s) {
-    return do_launch(twoshot_kernel<T, W, false>, p, ctas, cfg.threads, cfg.emulate_ranks, s);
+    if (p.op == SUM || p.op == AVG)
+      return do_launch(twoshot_kernel<T, W, false, true>, p, ctas, cfg.threads, cfg.emulate_ranks, s);
+    if (!std::is_same<T, W>::value) return cudaErrorInvalidValue;
+    return do_launch(twoshot_kernel<T, T, false, false>, p, ctas, cfg.threads, cfg.emulate_ranks, s);
   }
 };
 
@@ -623,10 +702,13 @@ int clamp_ctas(int ctas, const LaunchCfg& cfg) {
 }  // namespace
 
 int pick_ctas(size_t bytes, int ws, int requested) {
+  // `bytes` is what one rank pushes over the links; one CTA per 16 KiB of it
+  // (2 vectors per thread), up to the cap.  Small grids keep latency-bound
+  // messages cheap, large ones are needed to fill NVLink.
   (void)ws;
-  int cap = requested > 0 ? requested : 64;
+  int cap = requested > 0 ? requested : 128;
   if (cap > kMaxCtas) cap = kMaxCtas;
-  size_t want = (bytes + (64u << 10) - 1) / (64u << 10);  // one CTA per 64 KiB
+  size_t want = (bytes + (16u << 10) - 1) / (16u << 10);
   if (want < 1) want = 1;
   if (want > static_cast<size_t>(cap)) want = cap;
   return static_cast<int>(want);
@@ -643,7 +725,7 @@ size_t twoshot_arena_bytes(size_t nbytes_wire, int ws) {
 
 cudaError_t launch_allreduce_oneshot(const CollParams& p, DType dtype, DType wire, LaunchCfg cfg,
                                      cudaStream_t s) {
-  int ctas = clamp_ctas(cfg.ctas > 0 ? cfg.ctas : pick_ctas(p.count * dtype_size(wire), p.ctx[0].ws, 0), cfg);
+  int ctas = clamp_ctas(cfg.ctas > 0 ? cfg.ctas : pick_ctas(p.count * dtype_size(wire) * (p.ctx[0].ws - 1), p.ctx[0].ws, 0), cfg);
   return dispatch_types<OneShotL>(dtype, wire, p, ctas, cfg, s);
 }
 cudaError_t launch_allreduce_twoshot(const CollParams& p, DType dtype, DType wire, LaunchCfg cfg,

@@ -46,6 +46,12 @@ __device__ __forceinline__ bool epoch_reached(uint32_t seen, uint32_t want) {
   return static_cast<int32_t>(seen - want) >= 0;
 }
 
+// Signal values are (epoch << 12) + count: pipelined kernels publish a running
+// tile count inside one epoch, plain kernels publish kSigDone.  Values grow
+// monotonically across epochs (4095 tiles per CTA per epoch at most).
+constexpr uint32_t kSigDone = 4095;
+__device__ __forceinline__ uint32_t sig_value(uint32_t seq, uint32_t count) { return (seq << 12) + count; }
+
 __device__ __forceinline__ uint32_t* entered_flag(char* arena, int src) {
   return reinterpret_cast<uint32_t*>(arena + kEnteredOffset) + src;
 }

@@ -76,8 +76,17 @@ template <> struct Traits<bool8> {
   static __device__ __forceinline__ Acc scale(Acc a, float) { return a; }
 };
 
+// OP value meaning "MIN, MAX or PRODUCT chosen at run time" (see apply_rt).
+constexpr int kRuntimeOp = 100;
+
 template <typename T, int OP> struct Reduce {
   using Acc = typename Traits<T>::Acc;
+  // Run-time choice among MIN / MAX / PRODUCT (the rarely used operators share
+  // one kernel instantiation; SUM and AVG have their own fast one).
+  static __device__ __forceinline__ Acc apply_rt(int op, Acc a, Acc b) {
+    const Acc mn = b < a ? b : a, mx = b > a ? b : a, pr = a * b;
+    return op == MIN ? mn : op == MAX ? mx : pr;
+  }
   static __device__ __forceinline__ Acc apply(Acc a, Acc b) {
     if (OP == SUM || OP == AVG) return a + b;
     if (OP == PRODUCT) return a * b;
@@ -87,6 +96,7 @@ template <typename T, int OP> struct Reduce {
 };
 template <int OP> struct Reduce<bool8, OP> {
   using Acc = uint32_t;
+  static __device__ __forceinline__ Acc apply_rt(int op, Acc a, Acc b) { return op == MAX ? (a | b) : (a & b); }
   static __device__ __forceinline__ Acc apply(Acc a, Acc b) {
     if (OP == SUM || OP == AVG || OP == MAX) return a | b;
     return a & b;
@@ -95,6 +105,10 @@ template <int OP> struct Reduce<bool8, OP> {
 // u8 arithmetic wraps modulo 256 like the tensor dtype does.
 template <int OP> struct Reduce<uint8_t, OP> {
   using Acc = uint32_t;
+  static __device__ __forceinline__ Acc apply_rt(int op, Acc a, Acc b) {
+    const Acc mn = b < a ? b : a, mx = b > a ? b : a, pr = (a * b) & 0xFFu;
+    return op == MIN ? mn : op == MAX ? mx : pr;
+  }
   static __device__ __forceinline__ Acc apply(Acc a, Acc b) {
     if (OP == SUM || OP == AVG) return (a + b) & 0xFFu;
     if (OP == PRODUCT) return (a * b) & 0xFFu;

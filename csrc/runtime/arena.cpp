@@ -88,6 +88,8 @@ SymmetricArena::~SymmetricArena() {
   }
   for (auto* s : status_)
     if (s) cudaFree(s);
+  for (auto* s : stamps_)
+    if (s) cudaFree(s);
   if (prev >= 0) cudaSetDevice(prev);
 }
 
@@ -141,11 +143,32 @@ void SymmetricArena::fill_params(kern::CollParams& p, uint32_t epoch) const {
     c.ws = ws_;
     for (int r = 0; r < kern::kMaxWorld; ++r) c.arena[r] = r < ws_ ? bases_[r] : nullptr;
     c.status = status_[i];
+    c.stamps = (stamps_on_ && i < static_cast<int>(stamps_.size())) ? stamps_[i] : nullptr;
   }
 }
 
 void SymmetricArena::read_status(uint32_t out[kern::kStatusWords], cudaStream_t stream, int r) const {
   MCCL_CUDA_CHECK(cudaMemcpyAsync(out, status_[emulated_ ? r : 0], kern::kStatusWords * sizeof(uint32_t),
+                                  cudaMemcpyDeviceToHost, stream));
+  MCCL_CUDA_CHECK(cudaStreamSynchronize(stream));
+}
+
+void SymmetricArena::enable_stamps(bool on) {
+  if (on && stamps_.empty()) {
+    for (size_t i = 0; i < status_.size(); ++i) {
+      unsigned long long* p = nullptr;
+      MCCL_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&p), kern::kStampSlots * sizeof(unsigned long long)));
+      MCCL_CUDA_CHECK(cudaMemset(p, 0, kern::kStampSlots * sizeof(unsigned long long)));
+      stamps_.push_back(p);
+    }
+  }
+  stamps_on_ = on;
+}
+
+void SymmetricArena::read_stamps(unsigned long long out[kern::kStampSlots], cudaStream_t stream, int r) const {
+  for (int i = 0; i < kern::kStampSlots; ++i) out[i] = 0;
+  if (stamps_.empty()) return;
+  MCCL_CUDA_CHECK(cudaMemcpyAsync(out, stamps_[emulated_ ? r : 0], kern::kStampSlots * sizeof(unsigned long long),
                                   cudaMemcpyDeviceToHost, stream));
   MCCL_CUDA_CHECK(cudaStreamSynchronize(stream));
 }

@@ -60,6 +60,9 @@ class SymmetricArena {
   // Copies the status block of rank r out (synchronous on `stream`).
   void read_status(uint32_t out[kern::kStatusWords], cudaStream_t stream, int r = 0) const;
   void clear_status(cudaStream_t stream);
+  // Phase-stamp capture (off by default): fill_params passes the buffer to the kernels.
+  void enable_stamps(bool on);
+  void read_stamps(unsigned long long out[kern::kStampSlots], cudaStream_t stream, int r = 0) const;
   char* base(int r) const { return bases_[r]; }
 
  private:
@@ -74,6 +77,8 @@ class SymmetricArena {
   std::vector<char*> bases_;       // [ws]; bases_[rank_] is the local allocation
   std::vector<bool> opened_;       // peers mapped through IPC (to close)
   std::vector<uint32_t*> status_;  // device status blocks (1 real, ws emulated)
+  std::vector<unsigned long long*> stamps_;
+  bool stamps_on_ = false;
 };
 
 }  // namespace mccl

@@ -33,8 +33,8 @@ class Tuner {
       // one-shot moves (ws-1)*N per GPU instead of 2*(ws-1)/ws*N: its advantage
       // (one flag round instead of two) holds up to a few hundred KiB.
       oneshot_max_[ws] = ws <= 2 ? (size_t(2) << 20) : ws <= 4 ? (size_t(512) << 10) : (size_t(256) << 10);
-      ctas_small_[ws] = 8;
-      ctas_large_[ws] = 64;
+      ctas_small_[ws] = 32;
+      ctas_large_[ws] = 128;
     }
   }
 
@@ -46,10 +46,10 @@ class Tuner {
   void set_oneshot_max_bytes(int ws, size_t v) { oneshot_max_[ws] = v; }
   size_t segment_bytes() const { return segment_bytes_; }
   void set_segment_bytes(size_t v) { segment_bytes_ = v; }
-  int ctas_for(int ws, size_t bytes, int requested) const {
+  // `pushed_bytes`: what one rank sends over the links for this launch.
+  int ctas_for(int ws, size_t pushed_bytes, int requested) const {
     if (requested > 0) return requested;
-    int cap = bytes <= oneshot_max_[ws] ? ctas_small_[ws] : ctas_large_[ws];
-    return kern::pick_ctas(bytes, ws, cap);
+    return kern::pick_ctas(pushed_bytes, ws, ctas_large_[ws]);
   }
   void set_ctas(int ws, int small, int large) {
     if (small > 0) ctas_small_[ws] = small;

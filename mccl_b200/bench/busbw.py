@@ -1,0 +1,149 @@
+"""Collective bus-bandwidth sweep: mccl vs torch's NCCL backend on the same GPUs.
+
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29520 \
+        -m mccl_b200.bench.busbw --ops allreduce,reduce_scatter,allgather,broadcast \
+        --dtypes fp32,bf16 --min-bytes 1024 --max-bytes 1073741824 --compare-nccl --out busbw.jsonl
+
+Method (as in NCCL-tests and the reference's tests/bench_busbw.py:57-137):
+``algbw = bytes / t`` and ``busbw = algbw * f`` with f = 2(n-1)/n for allreduce, (n-1)/n
+for reduce_scatter/allgather (bytes = the full gathered size) and 1 for broadcast.
+Timing: CUDA events around `iters` back-to-back calls after warm-up, max over ranks.
+Buffers rotate through a pool larger than the 126 MB L2, so no iteration finds its input
+in cache.  Run it with ``MCCL_ALGO=oneshot`` and ``MCCL_ALGO=twoshot`` to find the crossover
+that goes into a tuner file (``MCCL_TUNE_FILE``), and with ``MCCL_COMM_CTAS`` to size the grid.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+DTYPES = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}
+L2_BYTES = 126 << 20
+
+
+def bus_factor(op: str, n: int) -> float:
+    if op == "allreduce":
+        return 2.0 * (n - 1) / n
+    if op in ("reduce_scatter", "allgather"):
+        return (n - 1) / n
+    return 1.0
+
+
+def make_call(op, group, ws, rank, numel_total, dtype, dev, pool):
+    """Returns (list of zero-arg callables, payload bytes); one callable per pooled buffer."""
+    esz = torch.empty(0, dtype=dtype).element_size()
+    calls = []
+    if op == "allreduce":
+        for _ in range(pool):
+            t = torch.randn(numel_total, device=dev).to(dtype)
+            calls.append(lambda t=t: dist.all_reduce(t, group=group))
+        nbytes = numel_total * esz
+    elif op == "broadcast":
+        for _ in range(pool):
+            t = torch.randn(numel_total, device=dev).to(dtype)
+            calls.append(lambda t=t: dist.broadcast(t, 0, group=group))
+        nbytes = numel_total * esz
+    elif op == "allgather":
+        per = max(numel_total // ws, 1)
+        for _ in range(pool):
+            i = torch.randn(per, device=dev).to(dtype)
+            o = torch.empty(per * ws, device=dev, dtype=dtype)
+            calls.append(lambda i=i, o=o: dist.all_gather_into_tensor(o, i, group=group))
+        nbytes = per * ws * esz
+    elif op == "reduce_scatter":
+        per = max(numel_total // ws, 1)
+        for _ in range(pool):
+            i = torch.randn(per * ws, device=dev).to(dtype)
+            o = torch.empty(per, device=dev, dtype=dtype)
+            calls.append(lambda i=i, o=o: dist.reduce_scatter_tensor(o, i, group=group))
+        nbytes = per * ws * esz
+    else:
+        raise ValueError(op)
+    return calls, nbytes
+
+
+def time_calls(calls, iters, warmup, dev, sync_group):
+    for i in range(warmup):
+        calls[i % len(calls)]()
+    torch.cuda.synchronize()
+    dist.barrier(group=sync_group)
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for i in range(iters):
+        calls[i % len(calls)]()
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / iters
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=sync_group)
+    return float(t.item())
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ops", default="allreduce")
+    ap.add_argument("--dtypes", default="fp32")
+    ap.add_argument("--min-bytes", type=int, default=1024)
+    ap.add_argument("--max-bytes", type=int, default=1 << 30)
+    ap.add_argument("--compare-nccl", action="store_true")
+    ap.add_argument("--out", default="")
+    ap.add_argument("--quick", action="store_true", help="every other size, fewer iterations")
+    args = ap.parse_args(argv)
+
+    import mccl_b200 as mccl  # noqa: F401  (registers the backend)
+
+    rank = int(os.environ.get("RANK", "0"))
+    ws = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("mccl", rank=rank, world_size=ws, device_id=dev)
+    groups = {"mccl": None}
+    if args.compare_nccl:
+        groups["nccl"] = dist.new_group(backend="nccl")
+    sizes = []
+    b = args.min_bytes
+    while b <= args.max_bytes:
+        sizes.append(b)
+        b *= 4 if args.quick else 2
+    rows = []
+    for op in args.ops.split(","):
+        for dname in args.dtypes.split(","):
+            dtype = DTYPES[dname]
+            esz = torch.empty(0, dtype=dtype).element_size()
+            for nbytes_req in sizes:
+                numel = max(nbytes_req // esz, 1)
+                pool = max(1, min(16, (2 * L2_BYTES) // max(nbytes_req, 1)))
+                if nbytes_req >= L2_BYTES:
+                    pool = 2 if nbytes_req <= (256 << 20) else 1
+                iters = 200 if nbytes_req <= (1 << 20) else 50 if nbytes_req <= (64 << 20) else 10
+                if args.quick:
+                    iters = max(iters // 4, 5)
+                for gname, group in groups.items():
+                    calls, nbytes = make_call(op, group, ws, rank, numel, dtype, dev, pool)
+                    ms = time_calls(calls, iters, max(3, iters // 10), dev, groups["mccl"])
+                    algbw = nbytes / (ms * 1e-3) / 1e9
+                    row = {"op": op, "dtype": dname, "bytes": nbytes, "backend": gname, "n_gpus": ws,
+                           "us": round(ms * 1e3, 2), "algbw_gbs": round(algbw, 2),
+                           "busbw_gbs": round(algbw * bus_factor(op, ws), 2), "iters": iters}
+                    rows.append(row)
+                    if rank == 0:
+                        print(json.dumps(row), flush=True)
+                    del calls
+                torch.cuda.empty_cache()
+    if rank == 0 and args.out:
+        with open(args.out, "w") as f:
+            for r in rows:
+                f.write(json.dumps(r) + "\n")
+    dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,131 @@
+"""Real multi-GPU runs of the NVLink peer-memory data plane (one process per GPU).
+
+Worker source is serialised into child processes with a hard wall-clock limit
+(mccl_b200.utils.spawn).  Needs >= 2 CUDA devices; world sizes above the
+device count are skipped.
+"""
+import pytest
+import torch
+
+from mccl_b200.utils.spawn import run_workers
+
+pytestmark = [pytest.mark.gpu(count=2)]
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _world_sizes():
+    return [w for w in (2, 4, 8) if w <= max(_ngpu(), 2)]
+
+
+def _collectives_worker(rank, ws):
+    import torch, torch.distributed as dist
+    be = mccl.get_backend(device=device)
+    sizes = [1, 3, 1023, 4097, 70001, 262147, 2100001]
+    for dtype in (torch.float32, torch.bfloat16, torch.float16, torch.int64, torch.int32):
+        for n in sizes:
+            base = (torch.arange(n, device=device) % 17).to(dtype)
+            t = base * (rank + 1) if dtype.is_floating_point else base * (rank + 1)
+            dist.all_reduce(t)
+            want = (base.double() * sum(range(1, ws + 1)))
+            assert torch.allclose(t.double(), want, rtol=2e-2 if dtype != torch.float32 else 1e-6), (dtype, n)
+    assert be.data_plane() == "nvlink-p2p", be.data_plane()
+    # ops
+    for op, fn in ((dist.ReduceOp.MAX, max), (dist.ReduceOp.MIN, min)):
+        t = torch.full((5000,), float(rank), device=device)
+        dist.all_reduce(t, op=op)
+        assert t[0].item() == fn(range(ws))
+    t = torch.full((100001,), float(rank + 1), device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.AVG)
+    assert abs(t[0].item() - (ws + 1) / 2) < 1e-6
+    # bitwise identity across ranks
+    g = torch.Generator(device="cpu").manual_seed(rank)
+    x = torch.randn(300007, generator=g).to(device)
+    dist.all_reduce(x)
+    gathered = [torch.empty_like(x) for _ in range(ws)]
+    dist.all_gather(gathered, x)
+    for o in gathered:
+        assert torch.equal(o, gathered[0])
+    # broadcast from every root
+    for root in range(ws):
+        for n in (1, 4096, 1000003):
+            b = torch.arange(n, device=device, dtype=torch.float32) + root if rank == root else torch.zeros(n, device=device)
+            dist.broadcast(b, root)
+            assert b[n - 1].item() == n - 1 + root
+    # all_gather_into_tensor / reduce_scatter_tensor
+    inp = torch.full((70001,), float(rank), device=device)
+    out = torch.empty(70001 * ws, device=device)
+    dist.all_gather_into_tensor(out, inp)
+    assert [out[i * 70001].item() for i in range(ws)] == [float(i) for i in range(ws)]
+    rs_in = torch.arange(ws * 1001, device=device, dtype=torch.float32)
+    rs_out = torch.empty(1001, device=device)
+    dist.reduce_scatter_tensor(rs_out, rs_in)
+    assert torch.equal(rs_out, rs_in[rank * 1001:(rank + 1) * 1001] * ws)
+    lst = [torch.full((33,), float(rank * 10 + i), device=device) for i in range(ws)]
+    o2 = torch.empty(33, device=device)
+    dist.reduce_scatter(o2, lst)
+    assert o2[0].item() == sum(r * 10 + rank for r in range(ws))
+    dist.barrier()
+    # async burst: many outstanding works
+    works = []
+    ts = [torch.full((65536,), float(i), device=device) for i in range(24)]
+    for t in ts:
+        works.append(dist.all_reduce(t, async_op=True))
+    for w in works:
+        w.wait()
+    torch.cuda.synchronize()
+    assert all(ts[i][0].item() == i * ws for i in range(24))
+    m = mccl.get_metrics()
+    assert m.total_ops > 0 and m.total_bytes_sent > 0 and m.total_errors == 0
+
+
+@pytest.mark.parametrize("ws", _world_sizes())
+def test_collectives_over_nvlink(ws):
+    if ws > _ngpu():
+        pytest.skip("not enough GPUs")
+    run_workers(_collectives_worker, ws, device="cuda", timeout=240)
+
+
+def _ddp_worker(rank, ws):
+    import torch, torch.distributed as dist
+    from mccl_b200.parallel import wrap_ddp
+    from mccl_b200.optim import FusedAdamW
+    torch.manual_seed(42)
+    def make():
+        torch.manual_seed(42)
+        return torch.nn.Sequential(torch.nn.Linear(512, 2048), torch.nn.ReLU(), torch.nn.Linear(2048, 2048),
+                                   torch.nn.ReLU(), torch.nn.Linear(2048, 10)).to(device)
+    ref = make()
+    model = wrap_ddp(make(), device_ids=[device.index], bucket_cap_mb=4)
+    opt = FusedAdamW(model.parameters(), lr=1e-3)
+    ref_opt = torch.optim.AdamW(ref.parameters(), lr=1e-3)
+    g = torch.Generator().manual_seed(7)
+    for step in range(5):
+        xs = torch.randn(8 * ws, 512, generator=g)
+        ys = torch.randint(0, 10, (8 * ws,), generator=g)
+        # DDP on this rank's shard, no host sync between backward and step
+        opt.zero_grad()
+        loss = torch.nn.functional.cross_entropy(model(xs[rank * 8:(rank + 1) * 8].to(device)), ys[rank * 8:(rank + 1) * 8].to(device))
+        loss.backward()
+        opt.step()
+        # single-process reference on the full batch
+        ref_opt.zero_grad()
+        torch.nn.functional.cross_entropy(ref(xs.to(device)), ys.to(device)).backward()
+        ref_opt.step()
+    for p, q in zip(model.module.parameters(), ref.parameters()):
+        assert torch.allclose(p, q, rtol=1e-2, atol=3e-3), (p - q).abs().max()  # summation order differs from 1 process
+    # replicas identical
+    flat = torch.cat([p.detach().reshape(-1) for p in model.module.parameters()])
+    outs = [torch.empty_like(flat) for _ in range(ws)]
+    dist.all_gather(outs, flat)
+    for o in outs:
+        assert torch.equal(o, outs[0])
+
+
+@pytest.mark.parametrize("ws", _world_sizes())
+def test_ddp_matches_single_process(ws):
+    if ws > _ngpu():
+        pytest.skip("not enough GPUs")
+    run_workers(_ddp_worker, ws, device="cuda", timeout=240)
