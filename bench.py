@@ -158,7 +158,7 @@ def main():
     d2h_bytes = 4
 
     def train_step(x, y):
-        opt.zero_grad(set_to_none=False)
+        opt.zero_grad()  # set_to_none: DDP re-points grads at its bucket views, no memset pass
         loss = loss_fn(ddp(x), y)
         loss.backward()
         opt.step()

@@ -60,6 +60,7 @@ ProcessGroupMCCL::ProcessGroupMCCL(const c10::intrusive_ptr<c10d::Store>& store,
     int n = tuner_.load(tune);
     MCCL_INFO("tuner: %d fields loaded from %s", n, tune.c_str());
   }
+  if (env_int("MCCL_SEGMENT_BYTES", 0) >= (1 << 20)) tuner_.set_segment_bytes(static_cast<size_t>(env_int("MCCL_SEGMENT_BYTES", 0)));
   if (options_->oneshot_max_bytes >= 0)
     for (int ws = 0; ws <= kern::kMaxWorld; ++ws)
       tuner_.set_oneshot_max_bytes(ws, static_cast<size_t>(options_->oneshot_max_bytes));

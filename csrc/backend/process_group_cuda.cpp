@@ -23,7 +23,13 @@ namespace mccl {
 
 struct ProcessGroupMCCL::CudaState {
   c10::DeviceIndex dev = 0;
-  std::unique_ptr<c10::cuda::CUDAStream> comm;
+  // One communication stream per lane: epoch e launches on lanes[e % 2], so two
+  // consecutive collectives (two DDP buckets) overlap each other's sync gaps.
+  std::vector<c10::cuda::CUDAStream> lanes;
+  cudaEvent_t lane_done[kern::kNumLanes] = {nullptr, nullptr};   // recorded behind the lane's latest epoch
+  cudaStream_t lane_last[kern::kNumLanes] = {nullptr, nullptr};  // stream that epoch was launched on
+  bool lane_used[kern::kNumLanes] = {false, false};
+  cudaEvent_t join_ev = nullptr;
   cudaStream_t poll_stream = nullptr;
   std::unique_ptr<SymmetricArena> arena;
   bool p2p = false;
@@ -55,6 +61,9 @@ struct ProcessGroupMCCL::CudaState {
       cudaEventDestroy(p.end);
     }
     for (auto e : free_events) cudaEventDestroy(e);
+    for (auto e : lane_done)
+      if (e) cudaEventDestroy(e);
+    if (join_ev) cudaEventDestroy(join_ev);
     arena.reset();
     if (poll_stream) cudaStreamDestroy(poll_stream);
   }
@@ -76,7 +85,12 @@ void ProcessGroupMCCL::ensure_cuda(c10::DeviceIndex dev) {
   c10::cuda::CUDAGuard guard(dev);
   auto st = std::make_shared<CudaState>();
   st->dev = dev;
-  st->comm = std::make_unique<c10::cuda::CUDAStream>(c10::cuda::getStreamFromPool(/*isHighPriority=*/true, dev));
+  for (int l = 0; l < kern::kNumLanes; ++l) {
+    st->lanes.push_back(c10::cuda::getStreamFromPool(/*isHighPriority=*/true, dev));
+    MCCL_CUDA_CHECK(cudaEventCreateWithFlags(&st->lane_done[l], cudaEventDisableTiming));
+  }
+  MCCL_CHECK(st->lanes[0] != st->lanes[1], "stream pool returned one stream twice");
+  MCCL_CUDA_CHECK(cudaEventCreateWithFlags(&st->join_ev, cudaEventDisableTiming));
   MCCL_CUDA_CHECK(cudaStreamCreateWithFlags(&st->poll_stream, cudaStreamNonBlocking));
 
   const int ws = getSize();
@@ -134,7 +148,7 @@ std::vector<int64_t> ProcessGroupMCCL::last_phase_stamps() {
   std::lock_guard<std::mutex> g(cuda_mu_);
   if (!cuda_ || !cuda_->arena) return out;
   c10::cuda::CUDAGuard guard(cuda_->dev);
-  MCCL_CUDA_CHECK(cudaStreamSynchronize(cuda_->comm->stream()));
+  for (auto& l : cuda_->lanes) MCCL_CUDA_CHECK(cudaStreamSynchronize(l.stream()));
   unsigned long long st[kern::kStampSlots];
   cuda_->arena->read_stamps(st, cuda_->poll_stream);
   for (auto v : st) out.push_back(static_cast<int64_t>(v));
@@ -198,19 +212,6 @@ void ProcessGroupMCCL::device_health_check() {
 
 namespace {
 
-struct LaunchScope {
-  // Orders the communication stream behind the caller's stream and picks the
-  // stream the kernels go to.
-  c10::cuda::CUDAStream stream;
-  LaunchScope(c10::cuda::CUDAStream cur, c10::cuda::CUDAStream comm, at::cuda::CUDAEvent& fence, bool overlap)
-      : stream(overlap ? comm : cur) {
-    if (overlap) {
-      fence.record(cur);
-      fence.block(comm);
-    }
-  }
-};
-
 double ms_since(std::chrono::steady_clock::time_point t0) {
   return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
 }
@@ -227,25 +228,44 @@ double ms_since(std::chrono::steady_clock::time_point t0) {
   } while (0)
 
 // Shared prologue/epilogue of every arena collective.
+//
+// Stream discipline.  Every launch takes the next arena epoch e; its lane is
+// e % 2.  With overlap on, the launch goes to that lane's stream (or, for
+// `serial` collectives that reuse temporaries between launches, always to lane
+// stream 0); with overlap off, to the caller's current stream.  Whatever the
+// stream, epochs of one lane are kept in order by the lane_done events: a launch
+// on a stream other than the one its lane last used waits for that lane's event
+// first.  The kernels' buffer-reuse credit relies on exactly this ordering.
 struct CudaPath {
   ProcessGroupMCCL& pg;
   ProcessGroupMCCL::CudaState& cs;
   c10::intrusive_ptr<WorkMCCL> work;
   uint32_t seq;
-  c10::cuda::CUDAStream stream;
+  c10::cuda::CUDAStream caller;
+  c10::cuda::CUDAStream stream;  // stream of the current epoch (valid after params())
+  bool serial;
+  bool overlap;
+  int cur_lane = -1;
+  std::vector<cudaStream_t> used;
   cudaEvent_t ev_start = nullptr, ev_end = nullptr;
+  bool started = false;
   bool skip = false;
 
   CudaPath(ProcessGroupMCCL& pg_, c10d::OpType op, const char* name, uint64_t bytes, std::vector<at::Tensor> outs,
-           c10::DeviceIndex dev)
-      : pg(pg_), cs(*pg_.cuda_), seq(pg_.next_seq()), stream(c10::cuda::getCurrentCUDAStream(dev)) {
+           c10::DeviceIndex dev, bool serial_ = false)
+      : pg(pg_), cs(*pg_.cuda_), seq(pg_.next_seq()), caller(c10::cuda::getCurrentCUDAStream(dev)),
+        stream(c10::cuda::getCurrentCUDAStream(dev)), serial(serial_), overlap(pg_.options_->overlap_comm) {
     pg.check_alive(name);
     work = c10::make_intrusive<WorkMCCL>(pg.getRank(), op, seq, name, std::move(outs), /*stream_mode=*/true, dev);
     pg.metrics_.op_start(seq, name, bytes);
     pg.watchdog_->watch(seq, name);
     auto t0 = std::chrono::steady_clock::now();
-    LaunchScope scope(c10::cuda::getCurrentCUDAStream(dev), *cs.comm, cs.fence, pg.options_->overlap_comm);
-    stream = scope.stream;
+    if (overlap) {
+      // producer fence: both lanes wait for everything already queued on the caller's stream
+      cs.fence.record(caller);
+      for (auto& l : cs.lanes) cs.fence.block(l);
+      stream = cs.lanes[0];
+    }
     pg.metrics_.record_phase(seq, Metrics::Phase::SYNC, ms_since(t0));
     pg.metrics_.op_execute_start(seq);
     pg.watchdog_->touch(seq);
@@ -254,14 +274,37 @@ struct CudaPath {
       ev_start = cs.get_event();
       ev_end = cs.get_event();
     }
-    MCCL_CUDA_CHECK(cudaEventRecord(ev_start, stream.stream()));
     skip = pg.skip_next_launch_.exchange(false);
   }
 
+  // Records the lane event behind the work of the current epoch.
+  void close_epoch() {
+    if (cur_lane < 0) return;
+    MCCL_CUDA_CHECK(cudaEventRecord(cs.lane_done[cur_lane], stream.stream()));
+    cs.lane_last[cur_lane] = stream.stream();
+    cs.lane_used[cur_lane] = true;
+    cur_lane = -1;
+  }
+
+  // Takes the next epoch, selects its stream and returns the kernel parameters.
   kern::CollParams params() {
+    close_epoch();
     kern::CollParams p;
     std::memset(&p, 0, sizeof(p));
-    cs.arena->fill_params(p, cs.arena->next_epoch());
+    const uint32_t epoch = cs.arena->next_epoch();
+    cs.arena->fill_params(p, epoch);
+    const int lane = static_cast<int>(epoch % kern::kNumLanes);
+    stream = overlap ? (serial ? cs.lanes[0] : cs.lanes[lane]) : caller;
+    if (cs.lane_used[lane] && cs.lane_last[lane] != stream.stream())
+      MCCL_CUDA_CHECK(cudaStreamWaitEvent(stream.stream(), cs.lane_done[lane], 0));
+    cur_lane = lane;
+    bool seen = false;
+    for (auto u : used) seen = seen || u == stream.stream();
+    if (!seen) used.push_back(stream.stream());
+    if (!started) {
+      MCCL_CUDA_CHECK(cudaEventRecord(ev_start, stream.stream()));
+      started = true;
+    }
     p.scale = 1.0f;
     p.wait_ns = static_cast<unsigned long long>(pg.options_->device_wait_us) * 1000ull;
     p.tiles = static_cast<int>(pg.options_->tiles);
@@ -274,12 +317,24 @@ struct CudaPath {
     return c;
   }
 
+  // The tensor is used on the communication streams: tell the caching allocator.
   void keep(const at::Tensor& t) {
-    if (t.defined() && t.is_cuda() && stream != c10::cuda::getCurrentCUDAStream(cs.dev))
-      c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), stream);
+    if (!t.defined() || !t.is_cuda() || !overlap) return;
+    for (auto& l : cs.lanes) c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), l);
   }
 
   c10::intrusive_ptr<c10d::Work> finish(bool blocking = false) {
+    close_epoch();
+    if (!started) {  // no launch happened (nothing to do): complete on the caller's stream
+      stream = caller;
+      MCCL_CUDA_CHECK(cudaEventRecord(ev_start, stream.stream()));
+    }
+    // join: the stream of the last launch waits for the other streams this collective used
+    for (auto u : used) {
+      if (u == stream.stream()) continue;
+      MCCL_CUDA_CHECK(cudaEventRecord(cs.join_ev, u));
+      MCCL_CUDA_CHECK(cudaStreamWaitEvent(stream.stream(), cs.join_ev, 0));
+    }
     MCCL_CUDA_CHECK(cudaEventRecord(ev_end, stream.stream()));
     {
       std::lock_guard<std::mutex> g(cs.pending_mu);
@@ -420,7 +475,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allgather(at::Tensor& out_
   }
   c10::cuda::CUDAGuard guard(dev);
   std::vector<at::Tensor> outs = scatter_to ? *scatter_to : std::vector<at::Tensor>{out_flat};
-  CudaPath cp(*this, c10d::OpType::ALLGATHER, "mccl:all_gather", in.nbytes() * ws, outs, dev);
+  CudaPath cp(*this, c10d::OpType::ALLGATHER, "mccl:all_gather", in.nbytes() * ws, outs, dev, /*serial=*/true);
   at::Tensor flat = out_flat;
   if (scatter_to) {
     c10::cuda::CUDAStreamGuard sg(cp.stream);  // temporary belongs to the stream that uses it
@@ -485,7 +540,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_reduce_scatter(at::Tensor&
   const kern::DType dt = to_kern_dtype(out.scalar_type());
   const size_t esz = out.element_size();
   const int64_t n = out.numel();
-  CudaPath cp(*this, c10d::OpType::REDUCE_SCATTER, "mccl:reduce_scatter", in_flat.nbytes(), {out}, dev);
+  CudaPath cp(*this, c10d::OpType::REDUCE_SCATTER, "mccl:reduce_scatter", in_flat.nbytes(), {out}, dev, /*serial=*/true);
   cp.keep(in_flat);
   cp.keep(out);
   const size_t cap = cuda_->arena->parity_bytes();
@@ -575,8 +630,8 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::allreduce_topk(at::Tensor& grad
   at::Tensor scratch, pairs;
   if (p2p) {
     cp = std::make_unique<CudaPath>(*this, c10d::OpType::ALLREDUCE, "mccl:all_reduce_topk", pair_bytes * ws,
-                                    std::vector<at::Tensor>{grad}, dev);
-    stream = cp->stream.stream();
+                                    std::vector<at::Tensor>{grad}, dev, /*serial=*/true);
+    stream = cp->stream.stream();  // serial collectives run on lane stream 0 (or the caller's stream)
     cp->keep(grad);
     cp->keep(residual);
   } else {

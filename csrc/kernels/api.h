@@ -14,7 +14,9 @@ namespace kern {
 
 constexpr int kMaxWorld = 8;         // ranks sharing one NVSwitch domain
 constexpr int kMaxCtas = 128;        // upper bound on CTAs of one collective kernel
-constexpr int kNumPhases = 4;        // independent signal arrays per arena
+constexpr int kNumPhases = 4;        // independent signal arrays per lane
+constexpr int kNumLanes = 2;         // collectives of consecutive epochs may run concurrently (one per lane)
+constexpr int kNumParity = 4;        // data buffers per arena: epoch e uses buffer e % 4
 
 enum DType : int { F32 = 0, F64, F16, BF16, I32, I64, U8, BOOL, DTYPE_COUNT };
 enum RedOp : int { SUM = 0, AVG, MIN, MAX, PRODUCT, REDOP_COUNT };
@@ -29,17 +31,19 @@ inline size_t dtype_size(DType t) {
 }
 
 // ---- symmetric arena layout -------------------------------------------------
-// Every rank owns one arena:  [ signal pad | data parity 0 | data parity 1 ].
+// Every rank owns one arena:  [ signal pad | data buffer 0 | ... | data buffer 3 ].
+// Epoch e runs in lane e % 2 (lanes map to two communication streams, so two
+// consecutive collectives overlap) and uses data buffer e % 4.
 // The signal pad holds 32-bit epoch flags, all written remotely with release
 // semantics and polled locally with acquire semantics:
-//   entered[src]              src has started collective `seq` (slot-reuse credit)
-//   sig[phase][cta][src]      src's CTA `cta` finished phase `phase` of `seq`
+//   entered[lane][src]        src has started epoch `seq` of that lane (buffer-reuse credit)
+//   sig[lane][phase][cta][src] src's CTA `cta` finished phase `phase` of `seq`
 // Flags only ever grow (the epoch is the process group's arena sequence
 // number), so they are never reset and a late reader can not miss a value.
 constexpr size_t kSignalBytes = 64 * 1024;
-constexpr size_t kEnteredOffset = 0;                         // u32[kMaxWorld]
-constexpr size_t kSigOffset = 256;                           // u32[kNumPhases][kMaxCtas][kMaxWorld]
-static_assert(kSigOffset + size_t(kNumPhases) * kMaxCtas * kMaxWorld * 4 <= kSignalBytes,
+constexpr size_t kEnteredOffset = 0;                         // u32[kNumLanes][kMaxWorld]
+constexpr size_t kSigOffset = 256;                           // u32[kNumLanes][kNumPhases][kMaxCtas][kMaxWorld]
+static_assert(kSigOffset + size_t(kNumLanes) * kNumPhases * kMaxCtas * kMaxWorld * 4 <= kSignalBytes,
               "signal pad too small");
 
 // Device status block (device memory, one per process group; the host reads it

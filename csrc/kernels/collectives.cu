@@ -116,15 +116,18 @@ struct CtaCtx {
   int cta, nctas, tid, nthreads;
 };
 
-// Announces "this rank has started epoch seq" to every peer and waits until
-// every peer has started epoch seq-1, i.e. has finished every access of epoch
-// seq-2, the previous user of this epoch's parity buffer.
+// Announces "this rank has started epoch seq" (in the epoch's lane) to every
+// peer and waits until every peer has started epoch seq-2 of the same lane.  A
+// lane is one stream, so a peer that has started seq-2 has finished seq-4, the
+// previous user of this epoch's data buffer (seq % 4): nothing of it is still
+// being read or written.  In steady state the wait is already satisfied.
 __device__ __forceinline__ bool enter_collective(const CtaCtx& k) {
   const RankCtx& c = *k.c;
   bool ok = true;
   if (k.tid < c.ws && k.tid != c.rank) {
-    if (k.cta == 0) st_release_sys(entered_flag(c.arena[k.tid], c.rank), k.p->seq);
-    ok = wait_epoch(entered_flag(c.arena[c.rank], k.tid), k.p->seq - 1, k.p->wait_ns, c.status, 100, k.tid);
+    const int lane = lane_of(k.p->seq);
+    if (k.cta == 0) st_release_sys(entered_flag(c.arena[k.tid], lane, c.rank), k.p->seq);
+    ok = wait_epoch(entered_flag(c.arena[c.rank], lane, k.tid), k.p->seq - 2, k.p->wait_ns, c.status, 100, k.tid);
   }
   if (k.tid == 0 && c.status != nullptr && *reinterpret_cast<volatile uint32_t*>(c.status) != 0u) ok = false;
   return __syncthreads_and(ok ? 1 : 0) != 0;
@@ -136,7 +139,7 @@ __device__ __forceinline__ void signal_all(const CtaCtx& k, int phase, uint32_t 
   __syncthreads();
   if (k.tid < c.ws) {
     fence_sys();
-    st_release_sys(sig_flag(c.arena[k.tid], phase, k.cta, c.rank), sig_value(k.p->seq, count));
+    st_release_sys(sig_flag(c.arena[k.tid], lane_of(k.p->seq), phase, k.cta, c.rank), sig_value(k.p->seq, count));
   }
 }
 __device__ __forceinline__ void signal_one(const CtaCtx& k, int phase, int dst) {
@@ -144,7 +147,7 @@ __device__ __forceinline__ void signal_one(const CtaCtx& k, int phase, int dst) 
   __syncthreads();
   if (k.tid == 0) {
     fence_sys();
-    st_release_sys(sig_flag(c.arena[dst], phase, k.cta, c.rank), sig_value(k.p->seq, kSigDone));
+    st_release_sys(sig_flag(c.arena[dst], lane_of(k.p->seq), phase, k.cta, c.rank), sig_value(k.p->seq, kSigDone));
   }
 }
 // Waits for the same CTA index of every rank (or of `only`, if >= 0).
@@ -152,7 +155,7 @@ __device__ __forceinline__ bool wait_all(const CtaCtx& k, int phase, int only = 
   const RankCtx& c = *k.c;
   bool ok = true;
   if (k.tid < c.ws && (only < 0 || k.tid == only))
-    ok = wait_epoch(sig_flag(c.arena[c.rank], phase, k.cta, k.tid), sig_value(k.p->seq, count), k.p->wait_ns, c.status,
+    ok = wait_epoch(sig_flag(c.arena[c.rank], lane_of(k.p->seq), phase, k.cta, k.tid), sig_value(k.p->seq, count), k.p->wait_ns, c.status,
                     static_cast<uint32_t>(phase), static_cast<uint32_t>(k.tid));
   return __syncthreads_and(ok ? 1 : 0) != 0;
 }
@@ -378,6 +381,7 @@ __device__ __forceinline__ void reduce_tile(const CtaCtx& k, const T* in_chunk, 
 // and the flag round trips overlap instead of forming three bulk-synchronous
 // phases.
 constexpr int kTileUnroll = 4;
+constexpr int kPullUnroll = 8;  // remote loads are round trips: keep more of them in flight
 
 // kSum: SUM/AVG (AVG differs only by the scale); otherwise MIN/MAX/PRODUCT at run time.
 template <typename T, typename W, bool kAllGather, bool kSum>
@@ -490,15 +494,15 @@ __global__ void __launch_bounds__(512) twoshot_kernel(const __grid_constant__ Co
         T* dst = out + static_cast<int64_t>(q) * chunk_elems;
         const int64_t dst_n = chunk_len(q);
         const bool al = is_aligned16(dst);
-        for (int64_t ub = u0; ub < u1; ub += batch_units) {
-          uint4 v[kTileUnroll];
+        for (int64_t ub = u0; ub < u1; ub += static_cast<int64_t>(k.nthreads) * kPullUnroll) {
+          uint4 v[kPullUnroll];
 #pragma unroll
-          for (int i = 0; i < kTileUnroll; ++i) {
+          for (int i = 0; i < kPullUnroll; ++i) {
             const int64_t u = ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
             if (u < u1) v[i] = ldg16(src + u * 16);
           }
 #pragma unroll
-          for (int i = 0; i < kTileUnroll; ++i) {
+          for (int i = 0; i < kPullUnroll; ++i) {
             const int64_t u = ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
             if (u < u1 && u * U::N < dst_n) {
               if (U::kSame && al && (u + 1) * U::N <= dst_n) {

@@ -52,12 +52,13 @@ __device__ __forceinline__ bool epoch_reached(uint32_t seen, uint32_t want) {
 constexpr uint32_t kSigDone = 4095;
 __device__ __forceinline__ uint32_t sig_value(uint32_t seq, uint32_t count) { return (seq << 12) + count; }
 
-__device__ __forceinline__ uint32_t* entered_flag(char* arena, int src) {
-  return reinterpret_cast<uint32_t*>(arena + kEnteredOffset) + src;
+__device__ __forceinline__ int lane_of(uint32_t seq) { return static_cast<int>(seq & (kNumLanes - 1)); }
+__device__ __forceinline__ uint32_t* entered_flag(char* arena, int lane, int src) {
+  return reinterpret_cast<uint32_t*>(arena + kEnteredOffset) + lane * kMaxWorld + src;
 }
-__device__ __forceinline__ uint32_t* sig_flag(char* arena, int phase, int cta, int src) {
+__device__ __forceinline__ uint32_t* sig_flag(char* arena, int lane, int phase, int cta, int src) {
   return reinterpret_cast<uint32_t*>(arena + kSigOffset) +
-         (static_cast<size_t>(phase) * kMaxCtas + cta) * kMaxWorld + src;
+         ((static_cast<size_t>(lane) * kNumPhases + phase) * kMaxCtas + cta) * kMaxWorld + src;
 }
 
 __device__ __forceinline__ void report_failure(uint32_t* status, uint32_t code, uint32_t seq,

@@ -305,8 +305,8 @@ __global__ void __launch_bounds__(512) topk_exchange_scatter_kernel(const __grid
   {
     bool ok = true;
     if (tid < c.ws && tid != c.rank) {
-      if (cta == 0) st_release_sys(entered_flag(c.arena[tid], c.rank), p.seq);
-      ok = wait_epoch(entered_flag(c.arena[c.rank], tid), p.seq - 1, p.wait_ns, c.status, 100, tid);
+      if (cta == 0) st_release_sys(entered_flag(c.arena[tid], lane_of(p.seq), c.rank), p.seq);
+      ok = wait_epoch(entered_flag(c.arena[c.rank], lane_of(p.seq), tid), p.seq - 2, p.wait_ns, c.status, 100, tid);
     }
     if (tid == 0 && c.status != nullptr && *reinterpret_cast<volatile uint32_t*>(c.status) != 0u) ok = false;
     if (!__syncthreads_and(ok ? 1 : 0)) return;
@@ -333,13 +333,13 @@ __global__ void __launch_bounds__(512) topk_exchange_scatter_kernel(const __grid
   __syncthreads();
   if (tid < c.ws) {
     fence_sys();
-    st_release_sys(sig_flag(c.arena[tid], 0, cta, c.rank), sig_value(p.seq, kSigDone));
+    st_release_sys(sig_flag(c.arena[tid], lane_of(p.seq), 0, cta, c.rank), sig_value(p.seq, kSigDone));
   }
   // Scatter needs every CTA's share of every list: wait for all (cta, rank) flags.
   {
     bool ok = true;
     for (int f = tid; f < nctas * c.ws; f += blockDim.x)
-      ok = ok && wait_epoch(sig_flag(c.arena[c.rank], 0, f / c.ws, f % c.ws), sig_value(p.seq, kSigDone), p.wait_ns, c.status, 0, f % c.ws);
+      ok = ok && wait_epoch(sig_flag(c.arena[c.rank], lane_of(p.seq), 0, f / c.ws, f % c.ws), sig_value(p.seq, kSigDone), p.wait_ns, c.status, 0, f % c.ws);
     if (!__syncthreads_and(ok ? 1 : 0)) return;
   }
   const uint2* lists[kMaxWorld];

@@ -33,7 +33,7 @@ SymmetricArena::SymmetricArena(int rank, int world_size, size_t parity_bytes)
   MCCL_CHECK(world_size >= 1 && world_size <= kern::kMaxWorld,
              "symmetric arena supports 1.." << kern::kMaxWorld << " ranks, got " << world_size);
   MCCL_CUDA_CHECK(cudaGetDevice(&device_));
-  total_bytes_ = kern::kSignalBytes + 2 * parity_bytes_;
+  total_bytes_ = kern::kSignalBytes + kern::kNumParity * parity_bytes_;
   bases_.assign(ws_, nullptr);
   opened_.assign(ws_, false);
   void* p = nullptr;
@@ -55,7 +55,7 @@ SymmetricArena* SymmetricArena::make_emulated(int world_size, size_t parity_byte
   a->ws_ = world_size;
   a->parity_bytes_ = parity_bytes;
   a->emulated_ = true;
-  a->total_bytes_ = kern::kSignalBytes + 2 * parity_bytes;
+  a->total_bytes_ = kern::kSignalBytes + kern::kNumParity * parity_bytes;
   MCCL_CUDA_CHECK(cudaGetDevice(&a->device_));
   a->bases_.assign(world_size, nullptr);
   a->opened_.assign(world_size, false);
@@ -134,7 +134,7 @@ std::string SymmetricArena::open_peers(const std::vector<std::string>& handles) 
 
 void SymmetricArena::fill_params(kern::CollParams& p, uint32_t epoch) const {
   p.seq = epoch;
-  p.parity_offset = kern::kSignalBytes + static_cast<size_t>(epoch & 1u) * parity_bytes_;
+  p.parity_offset = kern::kSignalBytes + static_cast<size_t>(epoch % kern::kNumParity) * parity_bytes_;
   p.parity_capacity = parity_bytes_;
   const int nctx = emulated_ ? ws_ : 1;
   for (int i = 0; i < nctx; ++i) {

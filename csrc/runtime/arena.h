@@ -1,7 +1,7 @@
 // SymmetricArena: the per-process-group block of device memory that peers write
 // into and read from directly over NVLink.
 //
-// Every rank allocates  [signal pad | parity buffer 0 | parity buffer 1]  with
+// Every rank allocates  [signal pad | data buffer 0..3]  with
 // cudaMalloc (outside torch's caching allocator, so the allocation is a whole
 // IPC-exportable block), zeroes the signal pad, publishes a
 // cudaIpcMemHandle through the c10d Store and maps every peer's block with
@@ -9,10 +9,11 @@
 // host and be P2P-capable; `open_peers` reports failure instead of throwing so
 // the process group can agree, collectively, to fall back to host staging.
 //
-// Collectives take consecutive epochs; epoch e uses parity buffer e & 1.  The
-// credit protocol in the kernels (enter_collective) guarantees that epoch e
-// never overwrites data a peer may still be reading from epoch e-2, so no
-// trailing barrier is needed and flags are never reset.
+// Collectives take consecutive epochs; epoch e runs in lane e % 2 (one stream
+// per lane, so two consecutive collectives overlap) and uses data buffer e % 4.
+// The credit protocol in the kernels (enter_collective) guarantees that epoch e
+// never touches a buffer a peer may still be using for epoch e-4, so no trailing
+// barrier is needed and flags are never reset.
 //
 // An emulation constructor builds `ws` arenas on ONE device for single-GPU
 // tests: the same kernels then run as one cooperative launch with grid.y = ws.

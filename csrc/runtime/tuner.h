@@ -32,9 +32,9 @@ class Tuner {
     for (int ws = 0; ws <= kern::kMaxWorld; ++ws) {
       // one-shot moves (ws-1)*N per GPU instead of 2*(ws-1)/ws*N: its advantage
       // (one flag round instead of two) holds up to a few hundred KiB.
-      oneshot_max_[ws] = ws <= 2 ? (size_t(2) << 20) : ws <= 4 ? (size_t(512) << 10) : (size_t(256) << 10);
+      oneshot_max_[ws] = ws <= 4 ? (size_t(2) << 20) : (size_t(1) << 20);
       ctas_small_[ws] = 32;
-      ctas_large_[ws] = 128;
+      ctas_large_[ws] = 64;  // two lanes may run at once: 2 x 64 CTAs stay below the 148 SMs
     }
   }
 
