@@ -41,6 +41,7 @@ CUDA_SOURCES = [
     "kernels/topk.cu",
     "kernels/stft.cu",
     "kernels/adamw.cu",
+    "kernels/noalloc.cu",
 ]
 
 NVCC_FLAGS = [
