@@ -1,0 +1,48 @@
+"""Host runtime pieces in isolation: watchdog, engine, memory pool, metrics, options."""
+import datetime
+
+import torch.distributed as dist
+
+
+def test_watchdog_unarmed_entries_never_expire(native):
+    assert native._test_watchdog(50, False, 300) == 0   # watched but never touched: queued work is safe
+    assert native._test_watchdog(50, True, 300) == 1    # armed: fires exactly once
+
+
+def test_engine_runs_everything_and_reports_errors(native):
+    order, done, errs = native._test_engine(1, 4, 50, 5)
+    assert order == list(range(50)), "one worker = submission order"
+    assert done == 40 and errs == 10
+    order, done, errs = native._test_engine(3, 2, 40, 0)  # tiny queue: submitter blocks, nothing is lost
+    assert sorted(order) == list(range(40)) and done == 40 and errs == 0
+
+
+def test_memory_pool_reuse_and_trim(native):
+    first, second, reused, total, after_trim = native._test_mempool()
+    assert first >= 1_250_000 and first % 4096 == 0      # 25 % head-room, page aligned
+    assert reused and second == first                     # best fit reuses the freed buffer
+    assert total == first and after_trim == 0
+
+
+def test_options_object_is_honoured(native):
+    o = native.MCCLOptions(datetime.timedelta(seconds=30))
+    o.small_msg_threshold = 1234
+    o.algo = "twoshot"
+    pg = native.ProcessGroupMCCL(dist.HashStore(), 0, 1, o)
+    d = pg.describe()
+    assert "small_msg_threshold=1234" in d and "algo=twoshot" in d
+    assert pg.data_plane() == "local" and not pg.poisoned
+    m = pg.get_metrics()
+    assert m.total_ops == 0 and m.total_errors == 0
+    pg.shutdown()
+
+
+def test_metrics_summary_fields(native):
+    fields = ["total_ops", "total_bytes_sent", "total_bytes_recv", "total_errors", "avg_latency_ms",
+              "p50_latency_ms", "p99_latency_ms", "peak_throughput_gbps", "avg_sync_ms", "avg_network_ms",
+              "avg_reduce_ms", "avg_queue_wait_ms", "avg_execution_ms"]
+    pg = native._create_process_group(dist.HashStore(), 0, 1, datetime.timedelta(seconds=10))
+    m = pg.get_metrics()
+    for f in fields:
+        assert hasattr(m, f), f
+    pg.shutdown()
