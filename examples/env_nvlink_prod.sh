@@ -1,0 +1,9 @@
+#!/usr/bin/env bash
+# Environment preset for an 8x B200 NVSwitch node: source before torchrun.
+export MCCL_OVERLAP_COMM=${MCCL_OVERLAP_COMM:-1}     # collectives on the side streams
+export MCCL_ALGO=${MCCL_ALGO:-auto}                  # one-shot / two-shot from the tuner table
+export MCCL_LOG_LEVEL=${MCCL_LOG_LEVEL:-WARN}
+export MCCL_WATCHDOG_TIMEOUT_MS=${MCCL_WATCHDOG_TIMEOUT_MS:-300000}
+export DDP_BUCKET_MB=${DDP_BUCKET_MB:-25}
+# export MCCL_WIRE_DTYPE=bf16                        # fp32 gradients travel as bf16 (fused cast)
+# export MCCL_COMPRESSION=topk MCCL_TOPK_RATIO=0.01  # top-k gradients with error feedback

@@ -25,6 +25,7 @@ from typing import Any, Dict, Optional
 from .version import __version__, COMPATIBILITY_MATRIX
 from .config import MCCLConfig
 from .tuning import apply_thunderbolt_production_defaults, apply_nvlink_production_defaults
+from . import config, params, tuning, version  # noqa: F401  (submodules reachable as attributes)
 
 _active_config: Optional[MCCLConfig] = None
 _backend_registered: bool = False
