@@ -43,6 +43,8 @@ def parse_args():
     ap.add_argument("--bucket-mb", type=int, default=25)
     ap.add_argument("--no-fused-hook", action="store_true", help="stock DDP divide + SUM allreduce")
     ap.add_argument("--no-fused-optim", action="store_true", help="torch.optim.AdamW instead of the fused kernel")
+    ap.add_argument("--optim-in-backward", default="auto", choices=["auto", "on", "off"],
+                    help="AdamW per bucket right behind its allreduce (auto: when there is communication to hide it behind, i.e. world > 1)")
     return ap.parse_args()
 
 
@@ -132,13 +134,17 @@ def main():
     torch.manual_seed(42)
     model = MLP94M().to(dev)
     n_params = num_parameters(model)
+    in_bw = False
     if args.impl == "mccl":
         from mccl_b200.parallel import wrap_ddp
         from mccl_b200.optim import FusedAdamW
+        opt = (torch.optim.AdamW(model.parameters(), lr=1e-3, fused=True) if args.no_fused_optim
+               else FusedAdamW(model.parameters(), lr=1e-3))
+        want_bw = args.optim_in_backward == "on" or (args.optim_in_backward == "auto" and world > 1)
+        in_bw = want_bw and not (args.no_fused_optim or args.no_fused_hook)
         ddp = wrap_ddp(model, device_ids=[local_rank], bucket_cap_mb=args.bucket_mb,
-                       fused_average=not args.no_fused_hook, compression="none")
-        opt = (torch.optim.AdamW(ddp.parameters(), lr=1e-3, fused=True) if args.no_fused_optim
-               else FusedAdamW(ddp.parameters(), lr=1e-3))
+                       fused_average=not args.no_fused_hook, compression="none",
+                       optimizer_in_backward=opt if in_bw else None)
     else:
         from torch.nn.parallel import DistributedDataParallel
         ddp = DistributedDataParallel(model, device_ids=[local_rank], bucket_cap_mb=args.bucket_mb,
@@ -238,6 +244,7 @@ def main():
             "data_plane": plane,
             "fused_avg_hook": args.impl == "mccl" and not args.no_fused_hook,
             "fused_adamw": args.impl == "mccl" and not args.no_fused_optim,
+            "optimizer_in_backward": args.impl == "mccl" and in_bw,
         },
         "clocks": clocks,
         "e2e": {"value": round(e2e_value, 2), "unit": "samples/s", "ms_per_step": round(ms_e2e / args.steps, 4),

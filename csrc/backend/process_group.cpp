@@ -9,6 +9,7 @@
 #include "common/env.h"
 #include "common/log.h"
 #include "cpu/reduce.h"
+#include "p2p/nccl_p2p.h"
 #include "runtime/mempool.h"
 
 namespace mccl {
@@ -140,6 +141,11 @@ void ProcessGroupMCCL::shutdown() {
     if (transport_) transport_->shutdown();
   }
   abort_all_inflight("process group shut down");
+  {
+    std::lock_guard<std::mutex> g(nccl_mu_);
+    if (nccl_p2p_) nccl_p2p_->shutdown();
+    nccl_p2p_.reset();
+  }
   cuda_.reset();
 }
 
@@ -911,12 +917,32 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::barrier(const c10d::BarrierOpti
                      [this, timeout](uint32_t) { rendezvous_->barrier("pg", timeout); });
 }
 
+NcclP2P* ProcessGroupMCCL::ensure_nccl_p2p() {
+  if (env_str("MCCL_P2P", "nccl") == "host") return nullptr;
+  std::lock_guard<std::mutex> g(nccl_mu_);
+  if (!nccl_p2p_) {
+    try {
+      nccl_p2p_ = std::make_shared<NcclP2P>(store_, getRank(), getSize(), options_->timeout);
+    } catch (const std::exception& e) {
+      MCCL_WARN("NCCL p2p unavailable (%s); CUDA send/recv are staged through host memory", e.what());
+      return nullptr;
+    }
+  }
+  return nccl_p2p_.get();
+}
+
 c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::send(std::vector<at::Tensor>& tensors, int dst, int tag) {
   check_alive("send");
   check_single(tensors, "send");
   MCCL_CHECK_TENSOR(dst >= 0 && dst < getSize() && dst != getRank(), "send: bad destination rank " << dst);
   at::Tensor t = tensors[0];
   if (t.numel() == 0) return completed_work(c10d::OpType::SEND, {t}, &t);  // zero-size: no wire traffic
+  if (t.is_cuda()) {
+    if (NcclP2P* p2p = ensure_nccl_p2p()) {
+      metrics_.record_transport_bytes(t.nbytes(), 0);
+      return p2p->send(tensors, dst, tag);
+    }
+  }
   ensure_transport();
   at::Tensor host = t;
   if (t.is_cuda()) host = t.to(at::kCPU);  // synchronous device->host copy on the caller's stream
@@ -935,6 +961,12 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::recv(std::vector<at::Tensor>& t
   MCCL_CHECK_TENSOR(src >= 0 && src < getSize() && src != getRank(), "recv: bad source rank " << src);
   at::Tensor t = tensors[0];
   if (t.numel() == 0) return completed_work(c10d::OpType::RECV, {t}, &t);
+  if (t.is_cuda()) {
+    if (NcclP2P* p2p = ensure_nccl_p2p()) {
+      metrics_.record_transport_bytes(0, t.nbytes());
+      return p2p->recv(tensors, src, tag);
+    }
+  }
   ensure_transport();
   if (t.is_cuda()) {
     // Host-staged: receive into pinned memory, then copy to the device.

@@ -50,6 +50,8 @@
 #include "runtime/watchdog.h"
 #include "transport/host_transport.h"
 
+namespace mccl { class NcclP2P; }
+
 namespace mccl {
 
 class ProcessGroupMCCL : public c10d::Backend {
@@ -177,6 +179,10 @@ class ProcessGroupMCCL : public c10d::Backend {
   std::unique_ptr<HostEngine> p2p_engine_;         // send/recv: may overlap collectives
   std::unique_ptr<Watchdog> watchdog_;
   std::unique_ptr<HealthMonitor> health_;
+  // CUDA send/recv: NCCL p2p on a side stream (created on first use); MCCL_P2P=host stages through pinned memory instead
+  std::shared_ptr<NcclP2P> nccl_p2p_;
+  std::mutex nccl_mu_;
+  NcclP2P* ensure_nccl_p2p();
 
   std::mutex works_mu_;
   std::unordered_map<uint32_t, c10::weak_intrusive_ptr<WorkMCCL>> works_;

@@ -34,6 +34,7 @@ CPP_SOURCES = [
     "compression/compressor.cpp",
     "cpu/reduce.cpp",
     "transforms/stft.cpp",
+    "p2p/nccl_p2p.cpp",
 ]
 CUDA_SOURCES = [
     "kernels/ew.cu",
@@ -58,6 +59,21 @@ def sources():
         p = CSRC / rel
         if p.exists():
             out.append(str(p))
+    return out
+
+
+def nccl_include_dirs():
+    """nccl.h matching torch's bundled NCCL (only send/recv use it, through torch's ProcessGroupNCCL)."""
+    out = []
+    try:
+        import nvidia.nccl
+        for base in list(getattr(nvidia.nccl, "__path__", [])):
+            if (Path(base) / "include" / "nccl.h").exists():
+                out.append(str(Path(base) / "include"))
+    except Exception:
+        pass
+    if not out and Path("/usr/include/nccl.h").exists():
+        out.append("/usr/include")
     return out
 
 
@@ -95,7 +111,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         sources=sources(),
         extra_cflags=cflags,
         extra_cuda_cflags=NVCC_FLAGS,
-        extra_include_paths=[str(CSRC)],
+        extra_include_paths=[str(CSRC)] + nccl_include_dirs(),
         build_directory=str(BUILD_DIR),
         with_cuda=True,
         is_python_module=False,

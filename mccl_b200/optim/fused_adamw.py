@@ -24,6 +24,12 @@ class FusedAdamW(torch.optim.Optimizer):
             raise ValueError("invalid AdamW hyper-parameters")
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
         self._plans = {}
+        # DDP hands back bucket parameters as tensors that may be fresh Python objects: find ours by address
+        self._by_ptr = {p.data_ptr(): (p, g) for g in self.param_groups for p in g["params"]}
+        self._bw_cache = {}
+        self._bw_touched = []
+        self._bw_step = 0
+        self._bw_done = set()
 
     def _plan_for(self, gi: int, params):
         key = (gi, tuple(p.data_ptr() for p in params))
@@ -49,8 +55,14 @@ class FusedAdamW(torch.optim.Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
+        for own in self._bw_touched:  # updated inside backward: only their step counters are left to refresh
+            for p in own:
+                self.state[p]["step"].fill_(float(self._bw_step))
+                self._bw_done.add(id(p))
+        self._bw_touched = []
         for gi, group in enumerate(self.param_groups):
-            params = [p for p in group["params"] if p.grad is not None]
+            # parameters already updated inside backward (step_bucket) are skipped
+            params = [p for p in group["params"] if p.grad is not None and id(p) not in self._bw_done]
             if not params:
                 continue
             if not all(p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() for p in params):
@@ -68,8 +80,43 @@ class FusedAdamW(torch.optim.Optimizer):
                     s.fill_(float(step))  # host tensor, as torch.optim.AdamW keeps it by default
                 else:
                     self.state[p]["step"] = step
+        self._bw_done = set()
         return loss
+
+    # ---- per-bucket stepping (optimizer inside backward) -----------------------
+    def begin_step_in_backward(self) -> int:
+        """Advances the shared step counter once per iteration; returns the new step."""
+        self._bw_step = getattr(self, "_bw_step", None)
+        any_p = next(p for g in self.param_groups for p in g["params"])
+        st = self.state[any_p]
+        cur = int(st["step"].item()) if "step" in st else 0
+        self._bw_step = cur + 1
+        self._bw_done = set()
+        self._bw_touched = []
+        return self._bw_step
+
+    @torch.no_grad()
+    def step_bucket(self, key, params, grads) -> None:
+        """Updates ``params`` (one DDP bucket) from ``grads`` with one kernel launch.
+
+        ``key`` identifies the bucket (its index); the launch plan, the canonical parameter
+        objects and their group are cached per key, so the per-call host cost is one
+        dictionary lookup and one launch (this runs on the autograd thread).  All parameters
+        of a bucket must share one parameter group.  The ``step`` entries of the state are
+        refreshed by the next :meth:`step`.
+        """
+        ent = self._bw_cache.get(key)
+        if ent is None or ent[0] != params[0].data_ptr():
+            own = [self._by_ptr[p.data_ptr()][0] for p in params]
+            group = self._by_ptr[own[0].data_ptr()][1]
+            ent = (params[0].data_ptr(), own, group, self._plan_for(("bucket", key), own))
+            self._bw_cache[key] = ent
+        _, own, group, plan = ent
+        b1, b2 = group["betas"]
+        plan.step(grads, group["lr"], b1, b2, group["eps"], group["weight_decay"], self._bw_step, 1.0)
+        self._bw_touched.append(own)
 
     def load_state_dict(self, state_dict):
         super().load_state_dict(state_dict)
         self._plans.clear()  # state tensors were replaced
+        self._bw_cache.clear()

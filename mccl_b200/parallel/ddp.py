@@ -76,14 +76,49 @@ def topk_hook(state: TopKState, bucket: dist.GradBucket) -> torch.futures.Future
     return work.get_future().then(lambda f: f.value()[0])
 
 
+class OptimizerInBackward:
+    """State of :func:`optimizer_in_backward_hook`: the fused optimizer and the process group."""
+
+    def __init__(self, optimizer, process_group=None):
+        self.optimizer = optimizer
+        self.process_group = process_group
+
+
+def optimizer_in_backward_hook(state: OptimizerInBackward, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
+    """DDP comm hook: fused-average allreduce, then the bucket's AdamW update, both off the main stream.
+
+    The update of a bucket is enqueued behind that bucket's allreduce and runs while later
+    buckets are still being reduced and backward is still computing, so the optimizer step
+    leaves the critical path.  ``optimizer.step()`` afterwards only covers parameters that
+    were not updated here (none, normally).
+    """
+    buf = bucket.buffer()
+    backend = _backend_for(state.process_group, buf.device)
+    opt = state.optimizer
+    if bucket.index() == 0:
+        opt.begin_step_in_backward()
+    work = backend.allreduce_scaled(buf, 1.0 / backend.size())
+    params, grads, key = bucket.parameters(), bucket.gradients(), bucket.index()
+
+    def update(fut):
+        out = fut.value()[0]
+        opt.step_bucket(key, params, grads)
+        return out
+
+    return work.get_future().then(update)
+
+
 def wrap_ddp(module: torch.nn.Module, *, device_ids=None, bucket_cap_mb: Optional[int] = None,
              compression: Optional[str] = None, fused_average: bool = True, process_group=None,
-             **ddp_kwargs) -> DistributedDataParallel:
+             optimizer_in_backward=None, **ddp_kwargs) -> DistributedDataParallel:
     """``DistributedDataParallel`` with the backend's fused hooks installed.
 
     ``compression`` (default: ``MCCL_COMPRESSION``) selects ``"topk"`` for the
     compressed hook; otherwise, on CUDA, the fused-average hook replaces DDP's
     separate divide pass.  ``bucket_cap_mb`` defaults to ``DDP_BUCKET_MB`` or 25.
+    ``optimizer_in_backward`` takes a :class:`mccl_b200.optim.FusedAdamW` built over the
+    module's parameters: each bucket is then updated right behind its allreduce (see
+    :func:`optimizer_in_backward_hook`); keep calling ``optimizer.step()`` once per iteration.
     """
     if bucket_cap_mb is None:
         bucket_cap_mb = int(os.environ.get("DDP_BUCKET_MB", "25"))
@@ -92,7 +127,10 @@ def wrap_ddp(module: torch.nn.Module, *, device_ids=None, bucket_cap_mb: Optiona
                                   process_group=process_group, **ddp_kwargs)
     on_cuda = next(module.parameters()).is_cuda
     mode = compression if compression is not None else os.environ.get("MCCL_COMPRESSION", "none")
-    if on_cuda and mode == "topk":
+    if on_cuda and optimizer_in_backward is not None and mode != "topk":
+        ddp._mccl_oib_state = OptimizerInBackward(optimizer_in_backward, process_group)
+        ddp.register_comm_hook(ddp._mccl_oib_state, optimizer_in_backward_hook)
+    elif on_cuda and mode == "topk":
         ddp._mccl_topk_state = TopKState(process_group)
         ddp.register_comm_hook(ddp._mccl_topk_state, topk_hook)
     elif on_cuda and fused_average:

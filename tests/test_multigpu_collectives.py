@@ -129,3 +129,33 @@ def test_ddp_matches_single_process(ws):
     if ws > _ngpu():
         pytest.skip("not enough GPUs")
     run_workers(_ddp_worker, ws, device="cuda", timeout=240)
+
+
+def _oib_worker(rank, ws):
+    import torch, torch.distributed as dist
+    from mccl_b200.parallel import wrap_ddp
+    from mccl_b200.optim import FusedAdamW
+    def make():
+        torch.manual_seed(3)
+        return torch.nn.Sequential(torch.nn.Linear(256, 1024), torch.nn.GELU(), torch.nn.Linear(1024, 1024),
+                                   torch.nn.GELU(), torch.nn.Linear(1024, 16)).to(device)
+    a, b = make(), make()
+    opt_a = FusedAdamW(a.parameters(), lr=1e-3)
+    opt_b = FusedAdamW(b.parameters(), lr=1e-3)
+    da = wrap_ddp(a, device_ids=[device.index], bucket_cap_mb=1)                                 # step after backward
+    db = wrap_ddp(b, device_ids=[device.index], bucket_cap_mb=1, optimizer_in_backward=opt_b)    # step per bucket
+    g = torch.Generator().manual_seed(rank)
+    for _ in range(6):
+        x = torch.randn(16, 256, generator=g).to(device); y = torch.randint(0, 16, (16,), generator=g).to(device)
+        for d, o in ((da, opt_a), (db, opt_b)):
+            o.zero_grad(); torch.nn.functional.cross_entropy(d(x), y).backward(); o.step()
+    for p, q in zip(a.parameters(), b.parameters()):
+        assert torch.equal(p, q), (p - q).abs().max()
+    assert int(opt_b.state[next(b.parameters())]["step"].item()) == 6
+    sd = opt_b.state_dict()   # same layout as torch.optim.AdamW: loads into it
+    ref = torch.optim.AdamW(b.parameters(), lr=1e-3); ref.load_state_dict(sd)
+
+
+@pytest.mark.parametrize("ws", [2])
+def test_optimizer_in_backward_matches_regular_step(ws):
+    run_workers(_oib_worker, ws, device="cuda", timeout=240)
