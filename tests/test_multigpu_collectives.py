@@ -68,6 +68,19 @@ def _collectives_worker(rank, ws):
     dist.reduce_scatter(o2, lst)
     assert o2[0].item() == sum(r * 10 + rank for r in range(ws))
     dist.barrier()
+    # send / recv of CUDA tensors (NCCL p2p on a side stream), while an allreduce is in flight
+    nxt, prv = (rank + 1) % ws, (rank - 1) % ws
+    big = torch.ones(8_000_000, device=device)
+    w_ar = dist.all_reduce(big, async_op=True)
+    payload = torch.full((100003,), float(rank), device=device)
+    got = torch.empty(100003, device=device)
+    if rank % 2 == 0:
+        dist.send(payload, nxt); dist.recv(got, prv)
+    else:
+        dist.recv(got, prv); dist.send(payload, nxt)
+    w_ar.wait()
+    torch.cuda.synchronize()
+    assert got[0].item() == prv and got[-1].item() == prv and big[0].item() == ws
     # async burst: many outstanding works
     works = []
     ts = [torch.full((65536,), float(i), device=device) for i in range(24)]
