@@ -43,8 +43,9 @@ def parse_args():
     ap.add_argument("--bucket-mb", type=int, default=25)
     ap.add_argument("--no-fused-hook", action="store_true", help="stock DDP divide + SUM allreduce")
     ap.add_argument("--no-fused-optim", action="store_true", help="torch.optim.AdamW instead of the fused kernel")
-    ap.add_argument("--optim-in-backward", default="auto", choices=["auto", "on", "off"],
-                    help="AdamW per bucket right behind its allreduce (auto: when there is communication to hide it behind, i.e. world > 1)")
+    ap.add_argument("--optim-in-backward", default="off", choices=["on", "off"],
+                    help="AdamW per bucket right behind its allreduce instead of one step after backward "
+                         "(measured slower for this model: the per-bucket Python hook stalls the autograd thread)")
     return ap.parse_args()
 
 
@@ -140,7 +141,7 @@ def main():
         from mccl_b200.optim import FusedAdamW
         opt = (torch.optim.AdamW(model.parameters(), lr=1e-3, fused=True) if args.no_fused_optim
                else FusedAdamW(model.parameters(), lr=1e-3))
-        want_bw = args.optim_in_backward == "on" or (args.optim_in_backward == "auto" and world > 1)
+        want_bw = args.optim_in_backward == "on"
         in_bw = want_bw and not (args.no_fused_optim or args.no_fused_hook)
         ddp = wrap_ddp(model, device_ids=[local_rank], bucket_cap_mb=args.bucket_mb,
                        fused_average=not args.no_fused_hook, compression="none",
