@@ -29,7 +29,7 @@ import sys
 import threading
 import time
 
-BASELINE_SAMPLES_PER_S = {1: 78.3, 2: 134.2}  # reference's published numbers (Apple GPUs)
+REFERENCE_SAMPLES_PER_S = {1: 78.3, 2: 134.2}  # reference's published numbers (Apple GPUs)
 GLOBAL_BATCH = 256
 IN_FEATURES, CLASSES = 2048, 1000
 
@@ -215,7 +215,7 @@ def main():
     ms_per_step = ms_total / args.steps
     value = GLOBAL_BATCH / (ms_per_step / 1e3)
     e2e_value = GLOBAL_BATCH / ((ms_e2e / args.steps) / 1e3)
-    base = BASELINE_SAMPLES_PER_S.get(world)
+    base = REFERENCE_SAMPLES_PER_S.get(world)
     plane = "n/a"
     if args.impl == "mccl":
         import mccl_b200 as mccl

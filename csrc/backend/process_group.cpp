@@ -685,6 +685,20 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::allreduce_scaled(std::vector<at
                      });
 }
 
+c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::allreduce_scaled_then(std::vector<at::Tensor>& tensors, float scale,
+                                                                       std::function<void(cudaStream_t)> epilogue) {
+  check_alive("allreduce_scaled_then");
+  check_single(tensors, "allreduce_scaled_then");
+  at::Tensor& t = tensors[0];
+  MCCL_CHECK_TENSOR(t.is_cuda() && t.is_floating_point(), "allreduce_scaled_then: floating-point CUDA tensors only");
+  if (getSize() == 1 || t.numel() == 0) {
+    if (scale != 1.0f && t.numel() > 0) t.mul_(scale);
+    if (epilogue) epilogue(c10::cuda::getCurrentCUDAStream(t.device().index()).stream());
+    return completed_work(c10d::OpType::ALLREDUCE, {t}, &t);
+  }
+  return cuda_allreduce(t, c10d::ReduceOp::SUM, scale, std::move(epilogue));
+}
+
 c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::allreduce_coalesced(
     std::vector<at::Tensor>& tensors, const c10d::AllreduceCoalescedOptions& opts) {
   check_alive("allreduce_coalesced");

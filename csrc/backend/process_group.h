@@ -112,6 +112,10 @@ class ProcessGroupMCCL : public c10d::Backend {
   // SUM allreduce with a multiplier fused into the reduction epilogue (gradient
   // averaging without DDP's separate pre-division pass).
   c10::intrusive_ptr<c10d::Work> allreduce_scaled(std::vector<at::Tensor>& tensors, float scale);
+  // Same, then `epilogue(stream)` is enqueued right behind the reduction on the communication
+  // stream and covered by the returned Work (used to chain a bucket's optimizer kernel natively).
+  c10::intrusive_ptr<c10d::Work> allreduce_scaled_then(std::vector<at::Tensor>& tensors, float scale,
+                                                        std::function<void(cudaStream_t)> epilogue);
   // Test hook: next CUDA collective is skipped on this rank (peers must time out).
   void test_skip_next_launch() { skip_next_launch_.store(true); }
   Tuner& tuner() { return tuner_; }
@@ -146,7 +150,8 @@ class ProcessGroupMCCL : public c10d::Backend {
 
   // ---- CUDA path (process_group_cuda.cpp) ----------------------------------
   void ensure_cuda(c10::DeviceIndex dev);
-  c10::intrusive_ptr<c10d::Work> cuda_allreduce(at::Tensor& t, c10d::ReduceOp::RedOpType op, float prescale);
+  c10::intrusive_ptr<c10d::Work> cuda_allreduce(at::Tensor& t, c10d::ReduceOp::RedOpType op, float prescale,
+                                                std::function<void(cudaStream_t)> epilogue = nullptr);
   c10::intrusive_ptr<c10d::Work> cuda_broadcast(at::Tensor& t, int root);
   c10::intrusive_ptr<c10d::Work> cuda_allgather(at::Tensor& out_flat, const at::Tensor& in,
                                                 std::vector<at::Tensor>* scatter_to);
@@ -157,6 +162,7 @@ class ProcessGroupMCCL : public c10d::Backend {
                                                  std::function<c10::intrusive_ptr<c10d::Work>(std::vector<at::Tensor>&)> fn,
                                                  bool copy_back);
   void poll_device();  // watchdog hook: status block + event-timed metrics
+  void drain_finished();
   void device_health_check();
 
   c10::intrusive_ptr<c10d::Store> store_;

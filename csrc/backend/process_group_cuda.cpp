@@ -155,34 +155,40 @@ std::vector<int64_t> ProcessGroupMCCL::last_phase_stamps() {
   return out;
 }
 
+// Retires collectives whose end event has fired: device time -> metrics, watchdog entry closed,
+// events back to the pool.  Never blocks.
+void ProcessGroupMCCL::drain_finished() {
+  if (!cuda_) return;
+  CudaState& cs = *cuda_;
+  std::lock_guard<std::mutex> pg(cs.pending_mu);
+  while (!cs.pending.empty()) {
+    auto& p = cs.pending.front();
+    cudaError_t q = cudaEventQuery(p.end);
+    if (q == cudaErrorNotReady) {
+      cudaGetLastError();
+      break;
+    }
+    float ms = 0.f;
+    if (q == cudaSuccess && cudaEventElapsedTime(&ms, p.start, p.end) != cudaSuccess) {
+      cudaGetLastError();
+      ms = 0.f;
+    }
+    metrics_.record_phase(p.seq, Metrics::Phase::NETWORK, ms);
+    metrics_.op_end_timed(p.seq, ms);
+    watchdog_->complete(p.seq);
+    cs.free_events.push_back(p.start);
+    cs.free_events.push_back(p.end);
+    cs.pending.pop_front();
+  }
+}
+
 void ProcessGroupMCCL::poll_device() {
   std::unique_lock<std::mutex> g(cuda_mu_, std::try_to_lock);
   if (!g.owns_lock() || !cuda_) return;
   CudaState& cs = *cuda_;
   c10::cuda::OptionalCUDAGuard guard(cs.dev);
   // 1. finished collectives -> metrics + watchdog
-  {
-    std::lock_guard<std::mutex> pg(cs.pending_mu);
-    while (!cs.pending.empty()) {
-      auto& p = cs.pending.front();
-      cudaError_t q = cudaEventQuery(p.end);
-      if (q == cudaErrorNotReady) {
-        cudaGetLastError();
-        break;
-      }
-      float ms = 0.f;
-      if (q == cudaSuccess && cudaEventElapsedTime(&ms, p.start, p.end) != cudaSuccess) {
-        cudaGetLastError();
-        ms = 0.f;
-      }
-      metrics_.record_phase(p.seq, Metrics::Phase::NETWORK, ms);
-      metrics_.op_end_timed(p.seq, ms);
-      watchdog_->complete(p.seq);
-      cs.free_events.push_back(p.start);
-      cs.free_events.push_back(p.end);
-      cs.pending.pop_front();
-    }
-  }
+  drain_finished();
   // 2. device status block (bounded waits that gave up)
   if (cs.arena && !poisoned_.load()) {
     uint32_t st[kern::kStatusWords] = {0};
@@ -250,6 +256,7 @@ struct CudaPath {
   cudaEvent_t ev_start = nullptr, ev_end = nullptr;
   bool started = false;
   bool skip = false;
+  std::function<void(cudaStream_t)> epilogue;  // enqueued behind the collective, covered by the Work
 
   CudaPath(ProcessGroupMCCL& pg_, c10d::OpType op, const char* name, uint64_t bytes, std::vector<at::Tensor> outs,
            c10::DeviceIndex dev, bool serial_ = false)
@@ -335,11 +342,18 @@ struct CudaPath {
       MCCL_CUDA_CHECK(cudaEventRecord(cs.join_ev, u));
       MCCL_CUDA_CHECK(cudaStreamWaitEvent(stream.stream(), cs.join_ev, 0));
     }
+    if (epilogue) {
+      c10::cuda::CUDAStreamGuard sg(stream);
+      epilogue(stream.stream());
+    }
     MCCL_CUDA_CHECK(cudaEventRecord(ev_end, stream.stream()));
+    bool crowded;
     {
       std::lock_guard<std::mutex> g(cs.pending_mu);
       cs.pending.push_back({seq, ev_start, ev_end});
+      crowded = cs.pending.size() > 64;
     }
+    if (crowded) pg.drain_finished();  // keep the event pool small between watchdog polls
     ProcessGroupMCCL* self = &pg;
     work->set_health_check([self] { self->device_health_check(); });
     work->attach_stream(stream, blocking || pg.options_->blocking_wait);
@@ -360,11 +374,12 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::staged_via_host(
 }
 
 c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allreduce(at::Tensor& t, c10d::ReduceOp::RedOpType op,
-                                                                float prescale) {
+                                                                float prescale,
+                                                                std::function<void(cudaStream_t)> epilogue) {
   const auto dev = t.device().index();
   ensure_cuda(dev);
   if (!cuda_->p2p) {
-    return staged_via_host(
+    auto w = staged_via_host(
         c10d::OpType::ALLREDUCE, {t},
         [this, op](std::vector<at::Tensor>& h) {
           c10d::AllreduceOptions o;
@@ -372,6 +387,9 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allreduce(at::Tensor& t, c
           return allreduce(h, o);
         },
         true);
+    if (prescale != 1.0f) t.mul_(prescale);
+    if (epilogue) epilogue(c10::cuda::getCurrentCUDAStream(dev).stream());
+    return w;
   }
   c10::cuda::CUDAGuard guard(dev);
   const int ws = getSize();
@@ -386,6 +404,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allreduce(at::Tensor& t, c
   const size_t wsz = kern::dtype_size(wire);
   const int64_t n = t.numel();
   CudaPath cp(*this, c10d::OpType::ALLREDUCE, "mccl:all_reduce", t.nbytes(), {t}, dev);
+  cp.epilogue = std::move(epilogue);
   cp.keep(t);
 
   // Segment so that every launch fits one parity buffer.

@@ -333,6 +333,13 @@ class AdamWPlan {
   // table is re-uploaded only when an address changed.
   void step(const std::vector<at::Tensor>& grads, double lr, double beta1, double beta2, double eps,
             double weight_decay, int64_t step, double grad_scale) {
+    bind_grads(grads);
+    c10::cuda::CUDAGuard guard(params_[0].device());
+    launch(at::cuda::getCurrentCUDAStream(), lr, beta1, beta2, eps, weight_decay, step, grad_scale);
+  }
+
+  // Points the plan at `grads` (uploads the pointer table only when an address changed).
+  void bind_grads(const std::vector<at::Tensor>& grads) {
     MCCL_CHECK_TENSOR(grads.size() == params_.size(), "AdamWPlan.step: expected one gradient per parameter");
     bool changed = false;
     for (size_t i = 0; i < grads.size(); ++i) {
@@ -346,12 +353,15 @@ class AdamWPlan {
         changed = true;
       }
     }
-    c10::cuda::CUDAGuard guard(params_[0].device());
-    auto stream = at::cuda::getCurrentCUDAStream();
     if (changed) {
+      c10::cuda::CUDAGuard guard(params_[0].device());
       at::Tensor host = at::tensor(grad_ptrs_, at::TensorOptions().dtype(at::kLong));
       d_g_.copy_(host);
     }
+  }
+
+  void launch(cudaStream_t stream, double lr, double beta1, double beta2, double eps, double weight_decay,
+              int64_t step, double grad_scale) {
     kern::AdamWTable tab;
     tab.params = reinterpret_cast<const uint64_t*>(d_p_.data_ptr<int64_t>());
     tab.grads = reinterpret_cast<const uint64_t*>(d_g_.data_ptr<int64_t>());
@@ -511,6 +521,21 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            },
            py::arg("tensor"), py::arg("scale"), py::call_guard<py::gil_scoped_release>())
       .def("last_phase_stamps", &ProcessGroupMCCL::last_phase_stamps, py::call_guard<py::gil_scoped_release>())
+      .def("allreduce_adamw",
+           [](ProcessGroupMCCL& pg, at::Tensor bucket, double scale, AdamWPlan& plan, std::vector<at::Tensor> grads,
+              double lr, double beta1, double beta2, double eps, double weight_decay, int64_t step) {
+             // bucket = sum(bucket) * scale in one kernel, then the bucket's AdamW update behind it on the
+             // same communication stream: no Python between the two, one Work covers both.
+             plan.bind_grads(grads);
+             std::vector<at::Tensor> v{bucket};
+             AdamWPlan* pl = &plan;
+             return pg.allreduce_scaled_then(v, static_cast<float>(scale), [=](cudaStream_t s) {
+               pl->launch(s, lr, beta1, beta2, eps, weight_decay, step, 1.0);
+             });
+           },
+           py::arg("bucket"), py::arg("scale"), py::arg("plan"), py::arg("grads"), py::arg("lr"), py::arg("beta1"),
+           py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("step"),
+           py::call_guard<py::gil_scoped_release>())
       .def("_test_skip_next_launch", &ProcessGroupMCCL::test_skip_next_launch)
       .def("shutdown", &ProcessGroupMCCL::shutdown, py::call_guard<py::gil_scoped_release>());
 

@@ -6,7 +6,7 @@
 // size, the largest payload for which the one-shot allreduce is faster than the
 // two-shot one, the CTA counts for both regimes and the two-shot segment size.
 // Defaults come from a bus-bandwidth sweep on 8x B200 (NVSwitch); `load()` reads
-// overrides written by the sweep tool (`python -m mccl_b200.bench.busbw --tune`)
+// overrides written by the sweep tool (`python -m mccl_b200.bench.busbw --tune FILE`)
 // as a flat JSON object of integer fields, e.g.
 //   {"ws8_oneshot_max_bytes": 524288, "ws8_ctas_large": 64, "segment_bytes": 67108864}
 // The path comes from MCCL_TUNE_FILE.  Every rank must load the same file: the
@@ -32,7 +32,9 @@ class Tuner {
     for (int ws = 0; ws <= kern::kMaxWorld; ++ws) {
       // one-shot moves (ws-1)*N per GPU instead of 2*(ws-1)/ws*N: its advantage
       // (one flag round instead of two) holds up to a few hundred KiB.
-      oneshot_max_[ws] = ws <= 4 ? (size_t(2) << 20) : (size_t(1) << 20);
+      // Measured crossovers (fp32, back-to-back calls): with 2 ranks both variants move N per
+      // direction, so the single flag round of one-shot wins at every size that fits the arena.
+      oneshot_max_[ws] = ws <= 2 ? (size_t(64) << 20) : ws <= 4 ? (size_t(4) << 20) : (size_t(1) << 20);
       ctas_small_[ws] = 32;
       ctas_large_[ws] = 64;  // two lanes may run at once: 2 x 64 CTAs stay below the 148 SMs
     }

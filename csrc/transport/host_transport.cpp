@@ -677,6 +677,7 @@ void HostTransport::reader_loop(int peer) {
         throw ProtocolError("frame with protocol version " + std::to_string(h.version));
       if (h.op == static_cast<uint8_t>(OpType::HEARTBEAT)) {
         bytes_recv_ += sizeof(h);
+        if (h.flags & FLAG_GOODBYE) p.departed = true;
         continue;
       }
       if (h.op == static_cast<uint8_t>(OpType::ABORT)) {
@@ -693,6 +694,10 @@ void HostTransport::reader_loop(int peer) {
     why = e.what();
   }
   if (stopping_.load()) notify = false;
+  if (p.departed.load()) {  // orderly shutdown of the peer: not a failure of this group
+    notify = false;
+    why = "peer shut down";
+  }
   fail_peer(peer, why.empty() ? "reader stopped" : why, notify);
 }
 
@@ -748,6 +753,19 @@ void HostTransport::shutdown() {
   bool e = false;
   if (!stopping_.compare_exchange_strong(e, true)) return;
   park_cv_.notify_all();
+  // 0. tell peers this is an orderly shutdown, so the EOF that follows is not reported as a failure
+  for (int pr = 0; pr < ws_; ++pr) {
+    if (pr == rank_) continue;
+    Peer& p = *peers_[pr];
+    if (p.fd < 0 || !p.connected.load()) continue;
+    MessageHeader h = make_header(OpType::HEARTBEAT, 0, 0, 0, 0, FLAG_LAST_CHUNK | FLAG_GOODBYE);
+    std::unique_lock<std::mutex> g(p.send_mu, std::try_to_lock);
+    if (!g.owns_lock()) continue;
+    try {
+      send_frame(p, h, nullptr);
+    } catch (...) {
+    }
+  }
   // 1. stop accepting, 2. half-close so peers see EOF, 3. join readers and close.
   if (listen_fd_ >= 0) {
     ::close(listen_fd_);

@@ -126,6 +126,7 @@ class HostTransport {
     std::string fail_reason;
     std::thread reader;
     std::atomic<int64_t> last_heard_ms{0};
+    std::atomic<bool> departed{false};  // peer announced an orderly shutdown
   };
 
   void reader_loop(int peer);

@@ -42,6 +42,7 @@ enum MsgFlags : uint8_t {
   FLAG_HAS_CRC = 1 << 0,
   FLAG_LAST_CHUNK = 1 << 1,
   FLAG_COMPRESSED = 1 << 2,
+  FLAG_GOODBYE = 1 << 3,  // on a HEARTBEAT frame: the sender is shutting down in an orderly way
 };
 
 #pragma pack(push, 1)

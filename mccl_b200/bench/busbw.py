@@ -10,7 +10,8 @@ for reduce_scatter/allgather (bytes = the full gathered size) and 1 for broadcas
 Timing: CUDA events around `iters` back-to-back calls after warm-up, max over ranks.
 Buffers rotate through a pool larger than the 126 MB L2, so no iteration finds its input
 in cache.  Run it with ``MCCL_ALGO=oneshot`` and ``MCCL_ALGO=twoshot`` to find the crossover
-that goes into a tuner file (``MCCL_TUNE_FILE``), and with ``MCCL_COMM_CTAS`` to size the grid.
+that goes into a tuner file, or let ``--tune FILE`` measure it (one-shot and two-shot pinned through
+``MCCLOptions`` on two extra groups) and write the file for ``MCCL_TUNE_FILE``; ``MCCL_COMM_CTAS`` sizes the grid.
 """
 from __future__ import annotations
 
@@ -85,6 +86,41 @@ def time_calls(calls, iters, warmup, dev, sync_group):
     return float(t.item())
 
 
+def tune(path, rank, ws, dev):
+    """Finds the one-shot / two-shot crossover for this world size and writes a tuner file.
+
+    Two extra process groups are created with the variant pinned through ``MCCLOptions``
+    (``pg_options`` are honoured by the backend); fp32 allreduce is timed from 16 KiB to
+    16 MiB and the largest size at which one-shot is at least as fast becomes
+    ``ws<N>_oneshot_max_bytes``.  Load the result with ``MCCL_TUNE_FILE`` on every rank.
+    """
+    import datetime
+
+    from mccl_b200 import _C
+    groups = {}
+    for algo in ("oneshot", "twoshot"):
+        o = _C.MCCLOptions(datetime.timedelta(seconds=120))
+        o.algo = algo
+        groups[algo] = dist.new_group(backend="mccl", pg_options=o)
+    best, rows, size = 0, [], 16 << 10
+    while size <= (16 << 20):
+        numel = size // 4
+        t = {}
+        for algo, g in groups.items():
+            calls, _ = make_call("allreduce", g, ws, rank, numel, torch.float32, dev, pool=8)
+            t[algo] = time_calls(calls, 40, 5, dev, None)
+        rows.append({"bytes": size, "oneshot_us": round(t["oneshot"] * 1e3, 2), "twoshot_us": round(t["twoshot"] * 1e3, 2)})
+        if t["oneshot"] <= t["twoshot"]:
+            best = size
+        if rank == 0:
+            print(json.dumps(rows[-1]), flush=True)
+        size *= 2
+    if rank == 0:
+        with open(path, "w") as f:
+            json.dump({f"ws{ws}_oneshot_max_bytes": best, "measured": rows}, f, indent=1)
+        print(f"wrote {path}: ws{ws}_oneshot_max_bytes = {best}", flush=True)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--ops", default="allreduce")
@@ -94,6 +130,7 @@ def main(argv=None):
     ap.add_argument("--compare-nccl", action="store_true")
     ap.add_argument("--out", default="")
     ap.add_argument("--quick", action="store_true", help="every other size, fewer iterations")
+    ap.add_argument("--tune", default="", help="measure one-shot vs two-shot allreduce and write a tuner file here")
     args = ap.parse_args(argv)
 
     import mccl_b200 as mccl  # noqa: F401  (registers the backend)
@@ -104,6 +141,10 @@ def main(argv=None):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("mccl", rank=rank, world_size=ws, device_id=dev)
+    if args.tune:
+        tune(args.tune, rank, ws, dev)
+        dist.destroy_process_group()
+        return 0
     groups = {"mccl": None}
     if args.compare_nccl:
         groups["nccl"] = dist.new_group(backend="nccl")

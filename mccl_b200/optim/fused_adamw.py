@@ -116,6 +116,19 @@ class FusedAdamW(torch.optim.Optimizer):
         plan.step(grads, group["lr"], b1, b2, group["eps"], group["weight_decay"], self._bw_step, 1.0)
         self._bw_touched.append(own)
 
+    def bucket_plan(self, key, params):
+        """``(plan, group)`` for one DDP bucket: the cached launch plan over the bucket's parameters."""
+        ent = self._bw_cache.get(key)
+        if ent is None or ent[0] != params[0].data_ptr():
+            own = [self._by_ptr[p.data_ptr()][0] for p in params]
+            group = self._by_ptr[own[0].data_ptr()][1]
+            ent = (params[0].data_ptr(), own, group, self._plan_for(("bucket", key), own))
+            self._bw_cache[key] = ent
+        return ent[3], ent[2], ent[1]
+
+    def mark_bucket_stepped(self, own) -> None:
+        self._bw_touched.append(own)
+
     def load_state_dict(self, state_dict):
         super().load_state_dict(state_dict)
         self._plans.clear()  # state tensors were replaced

@@ -82,30 +82,37 @@ class OptimizerInBackward:
     def __init__(self, optimizer, process_group=None):
         self.optimizer = optimizer
         self.process_group = process_group
+        self.backend = None   # resolved on first use
+        self.scale = 1.0
 
 
 def optimizer_in_backward_hook(state: OptimizerInBackward, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
     """DDP comm hook: fused-average allreduce, then the bucket's AdamW update, both off the main stream.
 
-    The update of a bucket is enqueued behind that bucket's allreduce and runs while later
-    buckets are still being reduced and backward is still computing, so the optimizer step
-    leaves the critical path.  ``optimizer.step()`` afterwards only covers parameters that
-    were not updated here (none, normally).
+    One native call per bucket enqueues the allreduce kernel and, right behind it on the same
+    communication stream, the AdamW kernel over the bucket's parameters; the returned future
+    covers both.  The update therefore runs while later buckets are still being reduced and
+    backward is still computing.  ``optimizer.step()`` afterwards only refreshes the step
+    counters (and covers parameters that were not updated here, normally none).
     """
     buf = bucket.buffer()
-    backend = _backend_for(state.process_group, buf.device)
+    backend = state.backend
+    if backend is None:
+        backend = state.backend = _backend_for(state.process_group, buf.device)
+        state.scale = 1.0 / backend.size()
     opt = state.optimizer
     if bucket.index() == 0:
         opt.begin_step_in_backward()
-    work = backend.allreduce_scaled(buf, 1.0 / backend.size())
-    params, grads, key = bucket.parameters(), bucket.gradients(), bucket.index()
+    plan, group, own = opt.bucket_plan(bucket.index(), bucket.parameters())
+    b1, b2 = group["betas"]
+    work = backend.allreduce_adamw(buf, state.scale, plan, bucket.gradients(), group["lr"], b1, b2, group["eps"],
+                                   group["weight_decay"], opt._bw_step)
+    opt.mark_bucket_stepped(own)
+    return work.get_future().then(_first_tensor)
 
-    def update(fut):
-        out = fut.value()[0]
-        opt.step_bucket(key, params, grads)
-        return out
 
-    return work.get_future().then(update)
+def _first_tensor(fut):
+    return fut.value()[0]
 
 
 def wrap_ddp(module: torch.nn.Module, *, device_ids=None, bucket_cap_mb: Optional[int] = None,
