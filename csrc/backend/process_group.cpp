@@ -116,7 +116,7 @@ std::string ProcessGroupMCCL::describe() const {
     << " overlap_comm=" << options_->overlap_comm << " arena=" << (options_->arena_bytes >> 20) << "MiB x2"
     << " oneshot_max(ws)=" << tuner_.oneshot_max_bytes(std::min(getSize(), kern::kMaxWorld))
     << " segment=" << (tuner_.segment_bytes() >> 20) << "MiB"
-    << " comm_ctas=" << options_->comm_ctas << " wire_dtype=" << options_->wire_dtype
+    << " lanes=" << options_->lanes << " comm_ctas=" << options_->comm_ctas << " wire_dtype=" << options_->wire_dtype
     << " compression=" << (compressor_ ? compressor_->name() : std::string("none"))
     << " topk_ratio=" << options_->topk_ratio << " watchdog_ms=" << options_->watchdog_timeout.count()
     << " heartbeat_ms=" << options_->heartbeat_interval.count()

@@ -261,7 +261,8 @@ struct CudaPath {
   CudaPath(ProcessGroupMCCL& pg_, c10d::OpType op, const char* name, uint64_t bytes, std::vector<at::Tensor> outs,
            c10::DeviceIndex dev, bool serial_ = false)
       : pg(pg_), cs(*pg_.cuda_), seq(pg_.next_seq()), caller(c10::cuda::getCurrentCUDAStream(dev)),
-        stream(c10::cuda::getCurrentCUDAStream(dev)), serial(serial_), overlap(pg_.options_->overlap_comm) {
+        stream(c10::cuda::getCurrentCUDAStream(dev)), serial(serial_ || pg_.options_->lanes < 2),
+        overlap(pg_.options_->overlap_comm) {
     pg.check_alive(name);
     work = c10::make_intrusive<WorkMCCL>(pg.getRank(), op, seq, name, std::move(outs), /*stream_mode=*/true, dev);
     pg.metrics_.op_start(seq, name, bytes);

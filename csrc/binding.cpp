@@ -157,7 +157,7 @@ class EmuGroup {
   }
 
   void allreduce(std::vector<at::Tensor> ts, const std::string& op, const std::string& algo,
-                 const std::string& wire, double scale, int ctas, int skip_rank) {
+                 const std::string& wire, double scale, int ctas, int tiles) {
     for (auto& t : ts) check_tensor(t, "emu allreduce");
     c10::cuda::CUDAGuard g(ts[0].device());
     kern::DType dt = to_kern_dtype(ts[0].scalar_type());
@@ -167,7 +167,7 @@ class EmuGroup {
     p.op = parse_op(op);
     p.scale = static_cast<float>((p.op == kern::AVG ? 1.0 / ws_ : 1.0) * scale);
     size_t wb = static_cast<size_t>(p.count) * kern::dtype_size(wd);
-    (void)skip_rank;
+    p.tiles = tiles;
     if (algo == "oneshot") {
       check_fits(kern::oneshot_arena_bytes(wb, ws_));
       CK(kern::launch_allreduce_oneshot(p, dt, wd, cfg(ctas), at::cuda::getCurrentCUDAStream()));
@@ -493,6 +493,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("algo", &MCCLOptions::algo)
       .def_readwrite("oneshot_max_bytes", &MCCLOptions::oneshot_max_bytes)
       .def_readwrite("comm_ctas", &MCCLOptions::comm_ctas)
+      .def_readwrite("tiles", &MCCLOptions::tiles)
+      .def_readwrite("lanes", &MCCLOptions::lanes)
       .def_readwrite("arena_bytes", &MCCLOptions::arena_bytes)
       .def_readwrite("device_wait_us", &MCCLOptions::device_wait_us)
       .def_readwrite("blocking_wait", &MCCLOptions::blocking_wait);
@@ -696,7 +698,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_property_readonly("world_size", &EmuGroup::world_size)
       .def("allreduce", &EmuGroup::allreduce, py::arg("tensors"), py::arg("op") = "sum",
            py::arg("algo") = "oneshot", py::arg("wire") = "none", py::arg("scale") = 1.0, py::arg("ctas") = 0,
-           py::arg("skip_rank") = -1)
+           py::arg("tiles") = 1)
       .def("reduce_scatter", &EmuGroup::reduce_scatter, py::arg("outputs"), py::arg("inputs"),
            py::arg("op") = "sum", py::arg("ctas") = 0)
       .def("allgather", &EmuGroup::allgather, py::arg("outputs"), py::arg("inputs"), py::arg("ctas") = 0)

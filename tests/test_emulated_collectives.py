@@ -227,3 +227,18 @@ def test_bounded_wait_reports_instead_of_hanging(native, cuda_device):
     g.allreduce(xs, "sum", "oneshot")
     torch.cuda.synchronize()
     assert xs[0][0].item() == ws
+
+
+@pytest.mark.parametrize("ws", [2, 4, 8])
+@pytest.mark.parametrize("tiles", [2, 3, 8])
+def test_twoshot_tile_pipeline_matches_bulk(native, cuda_device, ws, tiles):
+    # the software-pipelined form (push tile i, reduce i-1, pull i-2) must give the same bits as bulk phases
+    g = native.EmuGroup(ws, 16 << 20)
+    for n in (1000, 70001, 1_000_003):
+        xs = _inputs(ws, n, torch.float32, cuda_device, seed=n)
+        a = [x.clone() for x in xs]; b = [x.clone() for x in xs]
+        g.allreduce(a, "sum", "twoshot", "none", 1.0, 4, 1)
+        g.allreduce(b, "sum", "twoshot", "none", 1.0, 4, tiles)
+        torch.cuda.synchronize()
+        for r in range(ws):
+            assert torch.equal(a[r], b[r]) and torch.equal(b[r], b[0])

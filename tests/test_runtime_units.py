@@ -46,3 +46,27 @@ def test_metrics_summary_fields(native):
     for f in fields:
         assert hasattr(m, f), f
     pg.shutdown()
+
+
+def test_tuner_file_overrides(native, tmp_path, monkeypatch):
+    import json
+    f = tmp_path / "tune.json"
+    f.write_text(json.dumps({"ws8_oneshot_max_bytes": 524288, "ws8_ctas_large": 48, "segment_bytes": 33554432,
+                             "measured": [{"bytes": 1, "oneshot_us": 2.0}]}))
+    monkeypatch.setenv("MCCL_TUNE_FILE", str(f))
+    pg = native._create_process_group(dist.HashStore(), 0, 1, datetime.timedelta(seconds=10))
+    t = json.loads(pg.tuner_dump())
+    assert t["ws8_oneshot_max_bytes"] == 524288 and t["ws8_ctas_large"] == 48 and t["segment_bytes"] == 33554432
+    assert t["ws2_oneshot_max_bytes"] == 64 << 20   # untouched default
+    pg.shutdown()
+
+
+def test_collective_concurrency_caps_lanes(native, monkeypatch):
+    monkeypatch.setenv("MCCL_COLLECTIVE_CONCURRENCY", "1")
+    pg = native._create_process_group(dist.HashStore(), 0, 1, datetime.timedelta(seconds=10))
+    assert "lanes=1" in pg.describe()
+    pg.shutdown()
+    monkeypatch.delenv("MCCL_COLLECTIVE_CONCURRENCY")
+    pg = native._create_process_group(dist.HashStore(), 0, 1, datetime.timedelta(seconds=10))
+    assert "lanes=2" in pg.describe()
+    pg.shutdown()
