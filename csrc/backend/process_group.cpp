@@ -344,19 +344,6 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::submit_host(c10d::OpType op, co
 }
 
 // ---------------------------------------------------------------------------
-// compressed host messages: [4-byte size][payload]; the local contribution is
-// passed through the same codec so every rank reduces identical values.
-// ---------------------------------------------------------------------------
-void ProcessGroupMCCL::host_send_maybe_compressed(int peer, wire::OpType op, uint32_t seq, uint32_t tid,
-                                                  const at::Tensor& t) {
-  transport_->send(peer, op, seq, tid, t.data_ptr(), t.nbytes());
-}
-void ProcessGroupMCCL::host_recv_maybe_compressed(int peer, uint32_t seq, uint32_t tid, at::Tensor& t) {
-  auto tk = transport_->post_recv(peer, HostTransport::collective_key(seq, tid), t.data_ptr(), t.nbytes());
-  transport_->wait_recv(tk);
-}
-
-// ---------------------------------------------------------------------------
 // CPU algorithms
 // ---------------------------------------------------------------------------
 namespace {

@@ -145,8 +145,6 @@ class ProcessGroupMCCL : public c10d::Backend {
   void cpu_reduce_scatter(uint32_t seq, at::Tensor& out, std::vector<at::Tensor>& ins,
                           c10d::ReduceOp::RedOpType op);
   void cpu_reduce(uint32_t seq, at::Tensor& t, int root, c10d::ReduceOp::RedOpType op);
-  void host_send_maybe_compressed(int peer, OpType op, uint32_t seq, uint32_t tid, const at::Tensor& t);
-  void host_recv_maybe_compressed(int peer, uint32_t seq, uint32_t tid, at::Tensor& t);
 
   // ---- CUDA path (process_group_cuda.cpp) ----------------------------------
   void ensure_cuda(c10::DeviceIndex dev);

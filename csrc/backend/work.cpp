@@ -118,10 +118,6 @@ bool WorkMCCL::wait(std::chrono::milliseconds timeout) {
       }
       if (health_check_) health_check_();
     }
-    if (post_wait_ && !post_wait_done_) {
-      post_wait_done_ = true;
-      post_wait_();
-    }
     stash_.clear();
     return true;
   }

@@ -56,8 +56,6 @@ class WorkMCCL : public c10d::Work {
   }
   // Runs after the device work is known complete in a blocking wait; may throw.
   void set_health_check(std::function<void()> fn) { health_check_ = std::move(fn); }
-  // Copies results back (e.g. unflatten) on the caller's stream after the wait.
-  void set_post_wait(std::function<void()> fn) { post_wait_ = std::move(fn); }
 
   uint32_t seq() const { return seq_; }
   bool stream_mode() const { return stream_mode_; }
@@ -74,8 +72,6 @@ class WorkMCCL : public c10d::Work {
   std::unique_ptr<at::cuda::CUDAEvent> done_;
   c10::intrusive_ptr<c10::ivalue::Future> future_;
   std::function<void()> health_check_;
-  std::function<void()> post_wait_;
-  bool post_wait_done_ = false;
 };
 
 }  // namespace mccl

@@ -54,11 +54,6 @@ namespace {
     }                                                                             \
   } while (0)
 
-void require_native_cuda(const at::Tensor& t) {
-  // A CUDA tensor must be served by the sm_100a kernels; never fall back silently.
-  MCCL_CHECK(t.is_cuda() || t.is_cpu(), "tensor must be on cpu or cuda");
-}
-
 c10d::ReduceOp::RedOpType op_from_kern(kern::RedOp op) {
   switch (op) {
     case kern::SUM: return c10d::ReduceOp::SUM;
@@ -73,7 +68,6 @@ at::Tensor ew_binary(at::Tensor dst, const at::Tensor& src, kern::RedOp op) {
   check_tensor(dst, "elementwise");
   check_tensor(src, "elementwise");
   check_same(dst, src, "elementwise");
-  require_native_cuda(dst);
   if (dst.is_cuda()) {
     c10::cuda::CUDAGuard g(dst.device());
     CK(kern::launch_ew_reduce(dst.data_ptr(), src.data_ptr(), dst.numel(), to_kern_dtype(dst.scalar_type()), op,

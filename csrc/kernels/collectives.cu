@@ -142,14 +142,6 @@ __device__ __forceinline__ void signal_all(const CtaCtx& k, int phase, uint32_t 
     st_release_sys(sig_flag(c.arena[k.tid], lane_of(k.p->seq), phase, k.cta, c.rank), sig_value(k.p->seq, count));
   }
 }
-__device__ __forceinline__ void signal_one(const CtaCtx& k, int phase, int dst) {
-  const RankCtx& c = *k.c;
-  __syncthreads();
-  if (k.tid == 0) {
-    fence_sys();
-    st_release_sys(sig_flag(c.arena[dst], lane_of(k.p->seq), phase, k.cta, c.rank), sig_value(k.p->seq, kSigDone));
-  }
-}
 // Waits for the same CTA index of every rank (or of `only`, if >= 0).
 __device__ __forceinline__ bool wait_all(const CtaCtx& k, int phase, int only = -1, uint32_t count = kSigDone) {
   const RankCtx& c = *k.c;

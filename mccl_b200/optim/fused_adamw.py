@@ -61,7 +61,7 @@ class FusedAdamW(torch.optim.Optimizer):
                 self._bw_done.add(id(p))
         self._bw_touched = []
         for gi, group in enumerate(self.param_groups):
-            # parameters already updated inside backward (step_bucket) are skipped
+            # parameters already updated inside backward are skipped
             params = [p for p in group["params"] if p.grad is not None and id(p) not in self._bw_done]
             if not params:
                 continue
@@ -94,27 +94,6 @@ class FusedAdamW(torch.optim.Optimizer):
         self._bw_done = set()
         self._bw_touched = []
         return self._bw_step
-
-    @torch.no_grad()
-    def step_bucket(self, key, params, grads) -> None:
-        """Updates ``params`` (one DDP bucket) from ``grads`` with one kernel launch.
-
-        ``key`` identifies the bucket (its index); the launch plan, the canonical parameter
-        objects and their group are cached per key, so the per-call host cost is one
-        dictionary lookup and one launch (this runs on the autograd thread).  All parameters
-        of a bucket must share one parameter group.  The ``step`` entries of the state are
-        refreshed by the next :meth:`step`.
-        """
-        ent = self._bw_cache.get(key)
-        if ent is None or ent[0] != params[0].data_ptr():
-            own = [self._by_ptr[p.data_ptr()][0] for p in params]
-            group = self._by_ptr[own[0].data_ptr()][1]
-            ent = (params[0].data_ptr(), own, group, self._plan_for(("bucket", key), own))
-            self._bw_cache[key] = ent
-        _, own, group, plan = ent
-        b1, b2 = group["betas"]
-        plan.step(grads, group["lr"], b1, b2, group["eps"], group["weight_decay"], self._bw_step, 1.0)
-        self._bw_touched.append(own)
 
     def bucket_plan(self, key, params):
         """``(plan, group)`` for one DDP bucket: the cached launch plan over the bucket's parameters."""
