@@ -55,6 +55,8 @@ ProcessGroupMCCL::ProcessGroupMCCL(const c10::intrusive_ptr<c10d::Store>& store,
   if (std::getenv("MCCL_ALLREDUCE_ALGO"))
     MCCL_WARN("MCCL_ALLREDUCE_ALGO was removed: use MCCL_ALGO (auto|oneshot|twoshot|staged)");
 
+  device_timing_ = env_bool("MCCL_DEVICE_TIMING", true);
+  profile_titles_ = env_bool("MCCL_PROFILE_TITLES", false);
   compressor_ = make_compressor(options_->compression, options_->topk_ratio);
   std::string tune = env_str("MCCL_TUNE_FILE", "");
   if (!tune.empty()) {

@@ -172,6 +172,8 @@ class ProcessGroupMCCL : public c10d::Backend {
   std::string poison_reason_;
   std::atomic<bool> shut_down_{false};
   std::atomic<bool> skip_next_launch_{false};
+  bool device_timing_ = true;   // MCCL_DEVICE_TIMING: event pairs around every CUDA collective feed the metrics
+  bool profile_titles_ = false; // MCCL_PROFILE_TITLES: name the Work for torch's profiler (RecordFunction per op)
 
   Metrics metrics_;
   Tuner tuner_;

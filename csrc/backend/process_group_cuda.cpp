@@ -239,9 +239,15 @@ double ms_since(std::chrono::steady_clock::time_point t0) {
 // e % 2.  With overlap on, the launch goes to that lane's stream (or, for
 // `serial` collectives that reuse temporaries between launches, always to lane
 // stream 0); with overlap off, to the caller's current stream.  Whatever the
-// stream, epochs of one lane are kept in order by the lane_done events: a launch
-// on a stream other than the one its lane last used waits for that lane's event
-// first.  The kernels' buffer-reuse credit relies on exactly this ordering.
+// stream, epochs of one lane stay ordered: a launch on a stream other than the
+// one its lane last used first waits for an event recorded (at that moment) on
+// the lane's previous stream.  The kernels' buffer-reuse credit relies on
+// exactly this ordering.
+//
+// The host path is kept short because small collectives are bounded by it:
+// streams are fenced only when they are first used by the collective, device
+// timing events are recorded only when MCCL_DEVICE_TIMING is on, and the Work's
+// CUDA future is materialised only if somebody asks for it.
 struct CudaPath {
   ProcessGroupMCCL& pg;
   ProcessGroupMCCL::CudaState& cs;
@@ -251,44 +257,60 @@ struct CudaPath {
   c10::cuda::CUDAStream stream;  // stream of the current epoch (valid after params())
   bool serial;
   bool overlap;
+  bool timing;
+  bool fenced = false;           // producer event recorded on the caller's stream
   int cur_lane = -1;
-  std::vector<cudaStream_t> used;
+  cudaStream_t used[kern::kNumLanes + 1] = {nullptr, nullptr, nullptr};
+  int n_used = 0;
+  std::vector<at::Tensor> kept;
   cudaEvent_t ev_start = nullptr, ev_end = nullptr;
-  bool started = false;
   bool skip = false;
   std::function<void(cudaStream_t)> epilogue;  // enqueued behind the collective, covered by the Work
 
   CudaPath(ProcessGroupMCCL& pg_, c10d::OpType op, const char* name, uint64_t bytes, std::vector<at::Tensor> outs,
            c10::DeviceIndex dev, bool serial_ = false)
       : pg(pg_), cs(*pg_.cuda_), seq(pg_.next_seq()), caller(c10::cuda::getCurrentCUDAStream(dev)),
-        stream(c10::cuda::getCurrentCUDAStream(dev)), serial(serial_ || pg_.options_->lanes < 2),
-        overlap(pg_.options_->overlap_comm) {
+        stream(caller), serial(serial_ || pg_.options_->lanes < 2), overlap(pg_.options_->overlap_comm),
+        timing(pg_.device_timing_) {
     pg.check_alive(name);
-    work = c10::make_intrusive<WorkMCCL>(pg.getRank(), op, seq, name, std::move(outs), /*stream_mode=*/true, dev);
+    work = c10::make_intrusive<WorkMCCL>(pg.getRank(), op, seq, pg.profile_titles_ ? name : nullptr, std::move(outs),
+                                         /*stream_mode=*/true, dev);
     pg.metrics_.op_start(seq, name, bytes);
     pg.watchdog_->watch(seq, name);
-    auto t0 = std::chrono::steady_clock::now();
-    if (overlap) {
-      // producer fence: both lanes wait for everything already queued on the caller's stream
-      cs.fence.record(caller);
-      for (auto& l : cs.lanes) cs.fence.block(l);
-      stream = cs.lanes[0];
-    }
-    pg.metrics_.record_phase(seq, Metrics::Phase::SYNC, ms_since(t0));
-    pg.metrics_.op_execute_start(seq);
-    pg.watchdog_->touch(seq);
-    {
-      std::lock_guard<std::mutex> g(cs.pending_mu);
-      ev_start = cs.get_event();
-      ev_end = cs.get_event();
-    }
+    if (overlap && serial) use_stream(cs.lanes[0]);  // temporaries of serial collectives live on lane stream 0
     skip = pg.skip_next_launch_.exchange(false);
   }
 
-  // Records the lane event behind the work of the current epoch.
+  // First use of `s` by this collective: order it behind the producer and tell the allocator.
+  void use_stream(c10::cuda::CUDAStream s) {
+    stream = s;
+    for (int i = 0; i < n_used; ++i)
+      if (used[i] == s.stream()) return;
+    used[n_used++] = s.stream();
+    if (s != caller) {
+      if (!fenced) {
+        cs.fence.record(caller);
+        fenced = true;
+      }
+      cs.fence.block(s);
+      for (auto& t : kept) c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), s);
+    }
+    if (n_used == 1) {
+      pg.metrics_.op_execute_start(seq);
+      pg.watchdog_->touch(seq);
+      if (timing) {
+        {
+          std::lock_guard<std::mutex> g(cs.pending_mu);
+          ev_start = cs.get_event();
+          ev_end = cs.get_event();
+        }
+        MCCL_CUDA_CHECK(cudaEventRecord(ev_start, s.stream()));
+      }
+    }
+  }
+
   void close_epoch() {
     if (cur_lane < 0) return;
-    MCCL_CUDA_CHECK(cudaEventRecord(cs.lane_done[cur_lane], stream.stream()));
     cs.lane_last[cur_lane] = stream.stream();
     cs.lane_used[cur_lane] = true;
     cur_lane = -1;
@@ -302,21 +324,27 @@ struct CudaPath {
     const uint32_t epoch = cs.arena->next_epoch();
     cs.arena->fill_params(p, epoch);
     const int lane = static_cast<int>(epoch % kern::kNumLanes);
-    stream = overlap ? (serial ? cs.lanes[0] : cs.lanes[lane]) : caller;
-    if (cs.lane_used[lane] && cs.lane_last[lane] != stream.stream())
+    use_stream(overlap ? (serial ? cs.lanes[0] : cs.lanes[lane]) : caller);
+    if (cs.lane_used[lane] && cs.lane_last[lane] != stream.stream()) {
+      // the lane's previous epoch ran on another stream: order this one behind it
+      MCCL_CUDA_CHECK(cudaEventRecord(cs.lane_done[lane], cs.lane_last[lane]));
       MCCL_CUDA_CHECK(cudaStreamWaitEvent(stream.stream(), cs.lane_done[lane], 0));
-    cur_lane = lane;
-    bool seen = false;
-    for (auto u : used) seen = seen || u == stream.stream();
-    if (!seen) used.push_back(stream.stream());
-    if (!started) {
-      MCCL_CUDA_CHECK(cudaEventRecord(ev_start, stream.stream()));
-      started = true;
     }
+    cur_lane = lane;
     p.scale = 1.0f;
     p.wait_ns = static_cast<unsigned long long>(pg.options_->device_wait_us) * 1000ull;
     p.tiles = static_cast<int>(pg.options_->tiles);
     return p;
+  }
+
+  // Orders the current epoch's stream behind everything both lanes have been given so far
+  // (a barrier must not complete before earlier collectives of the group).
+  void wait_all_lanes() {
+    for (int l = 0; l < kern::kNumLanes; ++l)
+      if (cs.lane_used[l] && cs.lane_last[l] != stream.stream()) {
+        MCCL_CUDA_CHECK(cudaEventRecord(cs.lane_done[l], cs.lane_last[l]));
+        MCCL_CUDA_CHECK(cudaStreamWaitEvent(stream.stream(), cs.lane_done[l], 0));
+      }
   }
 
   kern::LaunchCfg cfg(size_t bytes) {
@@ -325,36 +353,43 @@ struct CudaPath {
     return c;
   }
 
-  // The tensor is used on the communication streams: tell the caching allocator.
+  // The tensor will be touched on the communication streams this collective uses.
   void keep(const at::Tensor& t) {
-    if (!t.defined() || !t.is_cuda() || !overlap) return;
-    for (auto& l : cs.lanes) c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), l);
+    if (!t.defined() || !t.is_cuda()) return;
+    kept.push_back(t);
+    for (int i = 0; i < n_used; ++i)
+      if (used[i] != caller.stream())
+        for (auto& l : cs.lanes)
+          if (l.stream() == used[i]) c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), l);
   }
 
   c10::intrusive_ptr<c10d::Work> finish(bool blocking = false) {
     close_epoch();
-    if (!started) {  // no launch happened (nothing to do): complete on the caller's stream
-      stream = caller;
-      MCCL_CUDA_CHECK(cudaEventRecord(ev_start, stream.stream()));
-    }
+    if (n_used == 0) use_stream(caller);  // nothing was launched: complete on the caller's stream
     // join: the stream of the last launch waits for the other streams this collective used
-    for (auto u : used) {
-      if (u == stream.stream()) continue;
-      MCCL_CUDA_CHECK(cudaEventRecord(cs.join_ev, u));
+    for (int i = 0; i < n_used; ++i) {
+      if (used[i] == stream.stream()) continue;
+      MCCL_CUDA_CHECK(cudaEventRecord(cs.join_ev, used[i]));
       MCCL_CUDA_CHECK(cudaStreamWaitEvent(stream.stream(), cs.join_ev, 0));
     }
     if (epilogue) {
       c10::cuda::CUDAStreamGuard sg(stream);
       epilogue(stream.stream());
     }
-    MCCL_CUDA_CHECK(cudaEventRecord(ev_end, stream.stream()));
-    bool crowded;
-    {
-      std::lock_guard<std::mutex> g(cs.pending_mu);
-      cs.pending.push_back({seq, ev_start, ev_end});
-      crowded = cs.pending.size() > 64;
+    if (timing) {
+      MCCL_CUDA_CHECK(cudaEventRecord(ev_end, stream.stream()));
+      bool crowded;
+      {
+        std::lock_guard<std::mutex> g(cs.pending_mu);
+        cs.pending.push_back({seq, ev_start, ev_end});
+        crowded = cs.pending.size() > 64;
+      }
+      if (crowded) pg.drain_finished();  // keep the event pool small between watchdog polls
+    } else {
+      // no device timing: the op is accounted with its host-side enqueue latency
+      pg.metrics_.op_end(seq);
+      pg.watchdog_->complete(seq);
     }
-    if (crowded) pg.drain_finished();  // keep the event pool small between watchdog polls
     ProcessGroupMCCL* self = &pg;
     work->set_health_check([self] { self->device_health_check(); });
     work->attach_stream(stream, blocking || pg.options_->blocking_wait);
@@ -606,6 +641,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_barrier() {
   c10::cuda::CUDAGuard guard(dev);
   CudaPath cp(*this, c10d::OpType::BARRIER, "mccl:barrier", 0, {}, dev);
   kern::CollParams p = cp.params();
+  cp.wait_all_lanes();
   if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_barrier(p, kern::LaunchCfg{}, cp.stream.stream()));
   return cp.finish(/*blocking=*/true);
 }

@@ -17,7 +17,9 @@ WorkMCCL::WorkMCCL(int rank, c10d::OpType op, uint32_t seq, const char* profilin
       outputs_(std::move(outputs)),
       stream_mode_(stream_mode),
       device_(device) {
-  ensure_future();  // created up front: engine threads and the caller both touch it
+  // Host works create their future up front (engine threads and the caller both touch it);
+  // stream works build it only if getFuture() is called.
+  if (!stream_mode_) ensure_future();
 }
 
 WorkMCCL::~WorkMCCL() = default;
@@ -37,14 +39,7 @@ void WorkMCCL::attach_stream(c10::cuda::CUDAStream comm, bool blocking_wait) {
   blocking_wait_ = blocking_wait;
   done_ = std::make_unique<at::cuda::CUDAEvent>(cudaEventDisableTiming);
   done_->record(comm);
-  ensure_future();
-  {
-    // Completing the future under the communication stream makes it record its
-    // own events there; consumers that only look at the future are then
-    // ordered after the collective kernel.
-    c10::cuda::CUDAStreamGuard g(comm);
-    future_->markCompleted(c10::IValue(outputs_));
-  }
+  comm_ = std::make_unique<c10::cuda::CUDAStream>(comm);
   {
     std::lock_guard<std::mutex> lk(mutex_);
     completed_ = true;  // "enqueued" is the completion notion of stream-ordered work
@@ -78,6 +73,11 @@ void WorkMCCL::mark_complete() {
 }
 
 void WorkMCCL::mark_error(const std::string& msg) {
+  if (stream_mode_) {  // enqueued work cannot be recalled; remember the error for wait()
+    std::lock_guard<std::mutex> lk(mutex_);
+    if (!exception_) exception_ = std::make_exception_ptr(MCCLError(msg));
+    return;
+  }
   ensure_future();
   std::exception_ptr ep = std::make_exception_ptr(MCCLError(msg));
   {
@@ -135,6 +135,17 @@ bool WorkMCCL::wait(std::chrono::milliseconds timeout) {
 void WorkMCCL::abort() { mark_error("operation aborted"); }
 
 c10::intrusive_ptr<c10::ivalue::Future> WorkMCCL::getFuture() {
+  if (stream_mode_ && !future_) {
+    ensure_future();
+    if (comm_) {
+      // Completing the future under the communication stream makes it record its own events
+      // there (everything enqueued so far, the collective included); consumers that only look
+      // at the future, like DDP's reducer, are then ordered after the kernel.
+      c10::cuda::CUDAStreamGuard g(*comm_);
+      future_->markCompleted(c10::IValue(outputs_));
+    }
+    return future_;
+  }
   ensure_future();
   return future_;
 }

@@ -70,6 +70,7 @@ class WorkMCCL : public c10d::Work {
   c10::DeviceIndex device_;
   bool blocking_wait_ = false;
   std::unique_ptr<at::cuda::CUDAEvent> done_;
+  std::unique_ptr<c10::cuda::CUDAStream> comm_;  // stream the collective was enqueued on
   c10::intrusive_ptr<c10::ivalue::Future> future_;
   std::function<void()> health_check_;
 };

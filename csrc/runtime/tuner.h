@@ -33,8 +33,8 @@ class Tuner {
       // one-shot moves (ws-1)*N per GPU instead of 2*(ws-1)/ws*N: its advantage
       // (one flag round instead of two) holds up to a few hundred KiB.
       // Measured crossovers (fp32, back-to-back calls): with 2 ranks both variants move N per
-      // direction, so the single flag round of one-shot wins at every size that fits the arena.
-      oneshot_max_[ws] = ws <= 2 ? (size_t(64) << 20) : ws <= 4 ? (size_t(4) << 20) : (size_t(1) << 20);
+      // direction, so the single flag round of one-shot wins up to 16 MiB (beyond that its extra HBM pass costs more).
+      oneshot_max_[ws] = ws <= 2 ? (size_t(16) << 20) : ws <= 4 ? (size_t(4) << 20) : (size_t(1) << 20);
       ctas_small_[ws] = 32;
       ctas_large_[ws] = 64;  // two lanes may run at once: 2 x 64 CTAs stay below the 148 SMs
     }

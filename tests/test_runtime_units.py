@@ -57,7 +57,7 @@ def test_tuner_file_overrides(native, tmp_path, monkeypatch):
     pg = native._create_process_group(dist.HashStore(), 0, 1, datetime.timedelta(seconds=10))
     t = json.loads(pg.tuner_dump())
     assert t["ws8_oneshot_max_bytes"] == 524288 and t["ws8_ctas_large"] == 48 and t["segment_bytes"] == 33554432
-    assert t["ws2_oneshot_max_bytes"] == 64 << 20   # untouched default
+    assert t["ws2_oneshot_max_bytes"] == 16 << 20   # untouched default
     pg.shutdown()
 
 
