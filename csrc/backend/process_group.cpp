@@ -55,7 +55,7 @@ ProcessGroupMCCL::ProcessGroupMCCL(const c10::intrusive_ptr<c10d::Store>& store,
   if (std::getenv("MCCL_ALLREDUCE_ALGO"))
     MCCL_WARN("MCCL_ALLREDUCE_ALGO was removed: use MCCL_ALGO (auto|oneshot|twoshot|staged)");
 
-  device_timing_ = env_bool("MCCL_DEVICE_TIMING", true);
+  device_timing_ = static_cast<int>(std::max<int64_t>(0, env_int("MCCL_DEVICE_TIMING", 8)));
   profile_titles_ = env_bool("MCCL_PROFILE_TITLES", false);
   compressor_ = make_compressor(options_->compression, options_->topk_ratio);
   std::string tune = env_str("MCCL_TUNE_FILE", "");

@@ -172,7 +172,11 @@ class ProcessGroupMCCL : public c10d::Backend {
   std::string poison_reason_;
   std::atomic<bool> shut_down_{false};
   std::atomic<bool> skip_next_launch_{false};
-  bool device_timing_ = true;   // MCCL_DEVICE_TIMING: event pairs around every CUDA collective feed the metrics
+  // MCCL_DEVICE_TIMING: 0 = never, 1 = every CUDA collective, N = every Nth (default 8).  Timed ops carry
+  // an event pair and feed the latency statistics; the others are only counted (timing events cost a few
+  // microseconds per call, which matters for latency-bound collectives).
+  int device_timing_ = 8;
+  std::atomic<uint32_t> timing_tick_{0};
   bool profile_titles_ = false; // MCCL_PROFILE_TITLES: name the Work for torch's profiler (RecordFunction per op)
 
   Metrics metrics_;

@@ -271,7 +271,7 @@ struct CudaPath {
            c10::DeviceIndex dev, bool serial_ = false)
       : pg(pg_), cs(*pg_.cuda_), seq(pg_.next_seq()), caller(c10::cuda::getCurrentCUDAStream(dev)),
         stream(caller), serial(serial_ || pg_.options_->lanes < 2), overlap(pg_.options_->overlap_comm),
-        timing(pg_.device_timing_) {
+        timing(pg_.device_timing_ > 0 && (pg_.timing_tick_++ % static_cast<uint32_t>(pg_.device_timing_)) == 0) {
     pg.check_alive(name);
     work = c10::make_intrusive<WorkMCCL>(pg.getRank(), op, seq, pg.profile_titles_ ? name : nullptr, std::move(outs),
                                          /*stream_mode=*/true, dev);
@@ -386,8 +386,7 @@ struct CudaPath {
       }
       if (crowded) pg.drain_finished();  // keep the event pool small between watchdog polls
     } else {
-      // no device timing: the op is accounted with its host-side enqueue latency
-      pg.metrics_.op_end(seq);
+      pg.metrics_.op_end_untimed(seq);  // counted, not part of the latency statistics
       pg.watchdog_->complete(seq);
     }
     ProcessGroupMCCL* self = &pg;

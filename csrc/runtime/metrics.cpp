@@ -80,6 +80,14 @@ void Metrics::op_end_timed(uint32_t seq, double execution_ms) {
   live_.erase(it);
 }
 
+void Metrics::op_end_untimed(uint32_t seq) {
+  std::lock_guard<std::mutex> g(mu_);
+  auto it = live_.find(seq);
+  if (it == live_.end()) return;
+  untimed_ops_++;
+  live_.erase(it);
+}
+
 void Metrics::record_transport_bytes(uint64_t sent, uint64_t recv) {
   std::lock_guard<std::mutex> g(mu_);
   bytes_sent_ += sent;
@@ -94,7 +102,7 @@ void Metrics::record_error() {
 Metrics::Summary Metrics::summarize() const {
   std::lock_guard<std::mutex> g(mu_);
   Summary s;
-  s.total_ops = total_ops_;
+  s.total_ops = total_ops_ + untimed_ops_;
   s.total_bytes_sent = bytes_sent_;
   s.total_bytes_recv = bytes_recv_;
   s.total_errors = errors_;
@@ -146,7 +154,7 @@ void Metrics::log_summary() const {
 void Metrics::reset() {
   std::lock_guard<std::mutex> g(mu_);
   history_.clear();
-  total_ops_ = bytes_sent_ = bytes_recv_ = errors_ = 0;
+  total_ops_ = untimed_ops_ = bytes_sent_ = bytes_recv_ = errors_ = 0;
   peak_gbps_ = 0;
   sum_latency_ = sum_sync_ = sum_net_ = sum_reduce_ = sum_queue_ = sum_exec_ = 0;
 }

@@ -59,6 +59,9 @@ class Metrics {
   void op_end(uint32_t seq);
   // Completion with externally measured (device) execution time.
   void op_end_timed(uint32_t seq, double execution_ms);
+  // Completion of an op whose device time was not sampled: counted (ops, bytes) but kept out of
+  // the latency statistics, which are over timed ops only.
+  void op_end_untimed(uint32_t seq);
   void record_transport_bytes(uint64_t sent, uint64_t recv);
   void record_error();
 
@@ -79,7 +82,7 @@ class Metrics {
   mutable std::mutex mu_;
   std::unordered_map<uint32_t, Live> live_;
   std::deque<OpRecord> history_;
-  uint64_t total_ops_ = 0, bytes_sent_ = 0, bytes_recv_ = 0, errors_ = 0;
+  uint64_t total_ops_ = 0, untimed_ops_ = 0, bytes_sent_ = 0, bytes_recv_ = 0, errors_ = 0;
   double peak_gbps_ = 0;
   // Running sums over all completed ops (not only the capped history).
   double sum_latency_ = 0, sum_sync_ = 0, sum_net_ = 0, sum_reduce_ = 0,
