@@ -61,6 +61,7 @@ struct MCCLOptions : c10d::Backend::Options {
   int64_t oneshot_max_bytes = -1;       // -1: tuner table
   int64_t comm_ctas = 0;                // 0: from message size
   int64_t tiles = 1;                    // two-shot pipeline tiles per CTA (1: bulk phases)
+  std::string gather = "auto";          // two-shot allreduce second half: auto (tuner) | pull | push
   int64_t lanes = 2;                    // collectives in flight at once on the arena (1 or 2)
   int64_t arena_bytes = 128ll << 20;    // one parity buffer
   int64_t device_wait_us = 60ll * 1000 * 1000;
@@ -88,6 +89,7 @@ struct MCCLOptions : c10d::Backend::Options {
     o->oneshot_max_bytes = env_int("MCCL_ONESHOT_MAX_BYTES", -1);
     o->comm_ctas = env_int("MCCL_COMM_CTAS", 0);
     o->tiles = env_int("MCCL_TILES", 1);
+    o->gather = env_str("MCCL_GATHER", "auto");
     // MCCL_COLLECTIVE_CONCURRENCY, when set, caps the lanes (1 = strictly one collective at a time)
     o->lanes = std::getenv("MCCL_COLLECTIVE_CONCURRENCY") ? std::min<int64_t>(2, collective_concurrency_requested()) : 2;
     o->arena_bytes = env_int("MCCL_ARENA_BYTES", 128ll << 20);

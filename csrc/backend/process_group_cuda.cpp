@@ -456,7 +456,10 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allreduce(at::Tensor& t, c
     if (options_->algo == "twoshot") v = Variant::TWOSHOT;
     if (v == Variant::ONESHOT && kern::oneshot_arena_bytes(wire_bytes, ws) > cap) v = Variant::TWOSHOT;
     MCCL_CHECK(kern::twoshot_arena_bytes(wire_bytes, ws) <= cap, "segment does not fit the arena");
+    bool push = options_->gather == "push" || (options_->gather == "auto" && tuner_.push_gather(ws));
+    if (push && kern::twoshot_arena_bytes(wire_bytes, ws, true) > cap) push = false;
     kern::CollParams p = cp.params();
+    p.push_gather = push ? 1 : 0;
     p.ctx[0].in = base + off * esz;
     p.ctx[0].out = base + off * esz;
     p.count = cnt;

@@ -151,7 +151,7 @@ class EmuGroup {
   }
 
   void allreduce(std::vector<at::Tensor> ts, const std::string& op, const std::string& algo,
-                 const std::string& wire, double scale, int ctas, int tiles) {
+                 const std::string& wire, double scale, int ctas, int tiles, bool push_gather) {
     for (auto& t : ts) check_tensor(t, "emu allreduce");
     c10::cuda::CUDAGuard g(ts[0].device());
     kern::DType dt = to_kern_dtype(ts[0].scalar_type());
@@ -162,11 +162,12 @@ class EmuGroup {
     p.scale = static_cast<float>((p.op == kern::AVG ? 1.0 / ws_ : 1.0) * scale);
     size_t wb = static_cast<size_t>(p.count) * kern::dtype_size(wd);
     p.tiles = tiles;
+    p.push_gather = push_gather ? 1 : 0;
     if (algo == "oneshot") {
       check_fits(kern::oneshot_arena_bytes(wb, ws_));
       CK(kern::launch_allreduce_oneshot(p, dt, wd, cfg(ctas), at::cuda::getCurrentCUDAStream()));
     } else {
-      check_fits(kern::twoshot_arena_bytes(wb, ws_));
+      check_fits(kern::twoshot_arena_bytes(wb, ws_, push_gather));
       CK(kern::launch_allreduce_twoshot(p, dt, wd, cfg(ctas), at::cuda::getCurrentCUDAStream()));
     }
   }
@@ -488,6 +489,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("oneshot_max_bytes", &MCCLOptions::oneshot_max_bytes)
       .def_readwrite("comm_ctas", &MCCLOptions::comm_ctas)
       .def_readwrite("tiles", &MCCLOptions::tiles)
+      .def_readwrite("gather", &MCCLOptions::gather)
       .def_readwrite("lanes", &MCCLOptions::lanes)
       .def_readwrite("arena_bytes", &MCCLOptions::arena_bytes)
       .def_readwrite("device_wait_us", &MCCLOptions::device_wait_us)
@@ -692,7 +694,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_property_readonly("world_size", &EmuGroup::world_size)
       .def("allreduce", &EmuGroup::allreduce, py::arg("tensors"), py::arg("op") = "sum",
            py::arg("algo") = "oneshot", py::arg("wire") = "none", py::arg("scale") = 1.0, py::arg("ctas") = 0,
-           py::arg("tiles") = 1)
+           py::arg("tiles") = 1, py::arg("push_gather") = false)
       .def("reduce_scatter", &EmuGroup::reduce_scatter, py::arg("outputs"), py::arg("inputs"),
            py::arg("op") = "sum", py::arg("ctas") = 0)
       .def("allgather", &EmuGroup::allgather, py::arg("outputs"), py::arg("inputs"), py::arg("ctas") = 0)

@@ -77,6 +77,7 @@ struct CollParams {
   float scale;             // multiplied into the result (1/world for AVG, DDP pre-division...)
   unsigned long long wait_ns;  // bound on every in-kernel wait
   int tiles;               // two-shot: pipeline tiles per CTA (<=1: bulk phases)
+  int push_gather;         // two-shot allreduce: owners push reduced chunks (needs 2x arena) instead of peers pulling
 };
 
 struct LaunchCfg {
@@ -90,7 +91,7 @@ int pick_ctas(size_t bytes, int ws, int requested);
 
 // Arena-size requirements (bytes of one parity buffer) for a payload.
 size_t oneshot_arena_bytes(size_t nbytes, int ws);
-size_t twoshot_arena_bytes(size_t nbytes, int ws);
+size_t twoshot_arena_bytes(size_t nbytes, int ws, bool push_gather = false);
 
 // All launchers return cudaSuccess or the launch error; none synchronises.
 // dtype: element type of in/out.  wire: element type stored in the arena

@@ -281,6 +281,10 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const __grid_con
 //            its own output
 //   phase 2  (allreduce only) pull: every rank loads the reduced chunks from
 //            the owners' arenas straight into its output tensor
+// With CollParams::push_gather the owner instead stores each reduced unit into
+// slot[ws + owner] of every peer from inside the reduction loop (link traffic
+// overlaps the HBM-bound reduction) and phase 2 is a local copy out of the arena;
+// that needs twice the arena space.
 // For reduce_scatter the "chunks" are the ws equal parts of the input list.
 // ---------------------------------------------------------------------------
 // Reduces units [u0, u1) of the chunk this rank owns.  G units are in flight per
@@ -348,8 +352,18 @@ __device__ __forceinline__ void reduce_tile_g(const CtaCtx& k, const T* in_chunk
       }
       if (keep_wire) {
         uint4 w = U::pack_W(acc);
-        stg16(local_buf + c.rank * slot_bytes + u * 16, w);
-        U::unpack_W(w, acc);  // the owner outputs exactly what the peers will pull
+        if (k.p->push_gather) {
+          // hand the reduced unit to every peer now: the stores ride the links while the
+          // next loads of this loop are in flight
+          for (int d = 1; d < c.ws; ++d) {
+            int q = c.rank + d;
+            if (q >= c.ws) q -= c.ws;
+            stg16(c.arena[q] + k.p->parity_offset + (c.ws + c.rank) * slot_bytes + u * 16, w);
+          }
+        } else {
+          stg16(local_buf + c.rank * slot_bytes + u * 16, w);
+        }
+        U::unpack_W(w, acc);  // the owner outputs exactly what the peers will receive
       }
       U::store_T(out_chunk, u * U::N, own_n, out_al, acc);
     }
@@ -482,7 +496,9 @@ __global__ void __launch_bounds__(512) twoshot_kernel(const __grid_constant__ Co
       for (int d = 1; d < c.ws; ++d) {
         int q = c.rank + d;
         if (q >= c.ws) q -= c.ws;
-        const char* src = c.arena[q] + p.parity_offset + q * slot_bytes;
+        // pull mode: the owner's arena over the link; push mode: the copy the owner left here
+        const char* src = p.push_gather ? local_buf + (c.ws + q) * slot_bytes
+                                        : c.arena[q] + p.parity_offset + q * slot_bytes;
         T* dst = out + static_cast<int64_t>(q) * chunk_elems;
         const int64_t dst_n = chunk_len(q);
         const bool al = is_aligned16(dst);
@@ -713,10 +729,10 @@ int pick_ctas(size_t bytes, int ws, int requested) {
 size_t oneshot_arena_bytes(size_t nbytes_wire, int ws) {
   return round_up(round_up(nbytes_wire, 16), 128) * ws;
 }
-size_t twoshot_arena_bytes(size_t nbytes_wire, int ws) {
+size_t twoshot_arena_bytes(size_t nbytes_wire, int ws, bool push_gather) {
   size_t units = (nbytes_wire + 15) / 16;
   size_t chunk_units = (units + ws - 1) / ws;
-  return round_up(chunk_units * 16, 128) * ws;
+  return round_up(chunk_units * 16, 128) * ws * (push_gather ? 2 : 1);
 }
 
 cudaError_t launch_allreduce_oneshot(const CollParams& p, DType dtype, DType wire, LaunchCfg cfg,

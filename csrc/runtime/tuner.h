@@ -37,6 +37,7 @@ class Tuner {
       oneshot_max_[ws] = ws <= 2 ? (size_t(16) << 20) : ws <= 4 ? (size_t(4) << 20) : (size_t(1) << 20);
       ctas_small_[ws] = 32;
       ctas_large_[ws] = 64;  // two lanes may run at once: 2 x 64 CTAs stay below the 148 SMs
+      push_gather_[ws] = 0;
     }
   }
 
@@ -46,6 +47,9 @@ class Tuner {
   }
   size_t oneshot_max_bytes(int ws) const { return oneshot_max_[ws]; }
   void set_oneshot_max_bytes(int ws, size_t v) { oneshot_max_[ws] = v; }
+  // Two-shot allreduce: owners push the reduced chunks (true) or peers pull them (false).
+  bool push_gather(int ws) const { return push_gather_[ws < 0 || ws > kern::kMaxWorld ? kern::kMaxWorld : ws] != 0; }
+  void set_push_gather(int ws, bool v) { push_gather_[ws] = v ? 1 : 0; }
   size_t segment_bytes() const { return segment_bytes_; }
   void set_segment_bytes(size_t v) { segment_bytes_ = v; }
   // `pushed_bytes`: what one rank sends over the links for this launch.
@@ -72,6 +76,7 @@ class Tuner {
       if (find_int(s, p + "oneshot_max_bytes", v) && v >= 0) { oneshot_max_[ws] = static_cast<size_t>(v); ++applied; }
       if (find_int(s, p + "ctas_small", v) && v > 0) { ctas_small_[ws] = static_cast<int>(v); ++applied; }
       if (find_int(s, p + "ctas_large", v) && v > 0) { ctas_large_[ws] = static_cast<int>(v); ++applied; }
+      if (find_int(s, p + "push_gather", v) && v >= 0) { push_gather_[ws] = v ? 1 : 0; ++applied; }
     }
     long long v;
     if (find_int(s, "segment_bytes", v) && v >= (1 << 20)) { segment_bytes_ = static_cast<size_t>(v); ++applied; }
@@ -85,6 +90,7 @@ class Tuner {
       o << "\"ws" << ws << "_oneshot_max_bytes\": " << oneshot_max_[ws] << ", ";
       o << "\"ws" << ws << "_ctas_small\": " << ctas_small_[ws] << ", ";
       o << "\"ws" << ws << "_ctas_large\": " << ctas_large_[ws] << ", ";
+      o << "\"ws" << ws << "_push_gather\": " << push_gather_[ws] << ", ";
     }
     o << "\"segment_bytes\": " << segment_bytes_ << "}";
     return o.str();
@@ -108,6 +114,7 @@ class Tuner {
   size_t oneshot_max_[kern::kMaxWorld + 1];
   int ctas_small_[kern::kMaxWorld + 1];
   int ctas_large_[kern::kMaxWorld + 1];
+  int push_gather_[kern::kMaxWorld + 1];
   size_t segment_bytes_ = size_t(64) << 20;
 };
 

@@ -242,3 +242,30 @@ def test_twoshot_tile_pipeline_matches_bulk(native, cuda_device, ws, tiles):
         torch.cuda.synchronize()
         for r in range(ws):
             assert torch.equal(a[r], b[r]) and torch.equal(b[r], b[0])
+
+
+@pytest.mark.parametrize("ws", [2, 3, 4, 8])
+@pytest.mark.parametrize("tiles", [1, 3])
+@pytest.mark.parametrize("dtype,wire", [(torch.float32, "none"), (torch.bfloat16, "none"), (torch.float32, "bf16")])
+def test_twoshot_push_gather_matches_pull(native, cuda_device, ws, tiles, dtype, wire):
+    # owners pushing the reduced chunks (second arena half + local copy) must give the same bits as
+    # peers pulling them; repeated so that buffer reuse across epochs is covered
+    g = native.EmuGroup(ws, 16 << 20)
+    for n in (1, 1000, 70001, 1_000_003):
+        for rep in range(3):
+            xs = _inputs(ws, n, dtype, cuda_device, seed=n + rep)
+            a = [x.clone() for x in xs]; b = [x.clone() for x in xs]
+            g.allreduce(a, "avg", "twoshot", wire, 1.0, 4, tiles, False)
+            g.allreduce(b, "avg", "twoshot", wire, 1.0, 4, tiles, True)
+            torch.cuda.synchronize()
+            for r in range(ws):
+                assert torch.equal(a[r], b[r]) and torch.equal(b[r], b[0])
+
+
+def test_twoshot_push_gather_needs_twice_the_arena(native, cuda_device):
+    g = native.EmuGroup(2, 1 << 20)
+    xs = _inputs(2, 200_000, torch.float32, cuda_device)  # 800 KB: fits once, not twice
+    g.allreduce([x.clone() for x in xs], "sum", "twoshot", "none", 1.0, 4, 1, False)
+    with pytest.raises(Exception, match="arena bytes"):
+        g.allreduce(xs, "sum", "twoshot", "none", 1.0, 4, 1, True)
+    torch.cuda.synchronize()

@@ -101,6 +101,36 @@ def test_collectives_over_nvlink(ws):
     run_workers(_collectives_worker, ws, device="cuda", timeout=240)
 
 
+def _push_gather_worker(rank, ws):
+    import torch, torch.distributed as dist
+    # two-shot with owners pushing the reduced chunks; back-to-back calls exercise both lanes and
+    # the reuse of the arena's second half
+    for dtype in (torch.float32, torch.bfloat16):
+        for n in (1, 4097, 262147, 2100001, 12_000_001):
+            for rep in range(3):
+                base = (torch.arange(n, device=device) % 13).to(dtype)
+                t = base * (rank + 1 + rep)
+                dist.all_reduce(t)
+                want = base.double() * sum(r + 1 + rep for r in range(ws))
+                assert torch.allclose(t.double(), want, rtol=2e-2 if dtype != torch.float32 else 1e-6), (dtype, n, rep)
+    g = torch.Generator(device="cpu").manual_seed(rank)
+    x = torch.randn(3_000_007, generator=g).to(device)
+    dist.all_reduce(x, op=dist.ReduceOp.AVG)
+    outs = [torch.empty_like(x) for _ in range(ws)]
+    dist.all_gather(outs, x)
+    for o in outs:
+        assert torch.equal(o, outs[0])
+    assert mccl.get_metrics().total_errors == 0
+
+
+@pytest.mark.parametrize("ws", _world_sizes())
+def test_twoshot_push_gather_over_nvlink(ws):
+    if ws > _ngpu():
+        pytest.skip("not enough GPUs")
+    run_workers(_push_gather_worker, ws, device="cuda", timeout=240,
+                env={"MCCL_GATHER": "push", "MCCL_ALGO": "twoshot"})
+
+
 def _ddp_worker(rank, ws):
     import torch, torch.distributed as dist
     from mccl_b200.parallel import wrap_ddp
