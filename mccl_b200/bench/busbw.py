@@ -92,7 +92,9 @@ def tune(path, rank, ws, dev):
     Two extra process groups are created with the variant pinned through ``MCCLOptions``
     (``pg_options`` are honoured by the backend); fp32 allreduce is timed from 16 KiB to
     16 MiB and the largest size at which one-shot is at least as fast becomes
-    ``ws<N>_oneshot_max_bytes``.  Load the result with ``MCCL_TUNE_FILE`` on every rank.
+    ``ws<N>_oneshot_max_bytes``.  The two forms of the two-shot second half (peers pull the
+    reduced chunks / owners push them) are then timed at 32 and 64 MiB; ``ws<N>_push_gather``
+    is 1 when pushing wins at both.  Load the result with ``MCCL_TUNE_FILE`` on every rank.
     """
     import datetime
 
@@ -115,10 +117,28 @@ def tune(path, rank, ws, dev):
         if rank == 0:
             print(json.dumps(rows[-1]), flush=True)
         size *= 2
+    gather_groups = {}
+    for mode in ("pull", "push"):
+        o = _C.MCCLOptions(datetime.timedelta(seconds=120))
+        o.algo = "twoshot"
+        o.gather = mode
+        gather_groups[mode] = dist.new_group(backend="mccl", pg_options=o)
+    push_wins, gather_rows = 0, []
+    for size in (32 << 20, 64 << 20):
+        t = {}
+        for mode, g in gather_groups.items():
+            calls, _ = make_call("allreduce", g, ws, rank, size // 4, torch.float32, dev, pool=4)
+            t[mode] = time_calls(calls, 20, 5, dev, None)
+        gather_rows.append({"bytes": size, "pull_us": round(t["pull"] * 1e3, 2), "push_us": round(t["push"] * 1e3, 2)})
+        push_wins += t["push"] < t["pull"]
+        if rank == 0:
+            print(json.dumps(gather_rows[-1]), flush=True)
+    push = int(push_wins == 2)
     if rank == 0:
         with open(path, "w") as f:
-            json.dump({f"ws{ws}_oneshot_max_bytes": best, "measured": rows}, f, indent=1)
-        print(f"wrote {path}: ws{ws}_oneshot_max_bytes = {best}", flush=True)
+            json.dump({f"ws{ws}_oneshot_max_bytes": best, f"ws{ws}_push_gather": push, "measured": rows,
+                       "measured_gather": gather_rows}, f, indent=1)
+        print(f"wrote {path}: ws{ws}_oneshot_max_bytes = {best}, ws{ws}_push_gather = {push}", flush=True)
 
 
 def main(argv=None):
