@@ -27,120 +27,23 @@
 namespace mccl {
 namespace kern {
 
-// Two-shot kernels, one translation unit per world-size class.
-cudaError_t launch_twoshot_ws2(bool allgather, const CollParams& p, DType dtype, DType wire, int ctas,
-                               const LaunchCfg& cfg, cudaStream_t s);
-cudaError_t launch_twoshot_ws4(bool allgather, const CollParams& p, DType dtype, DType wire, int ctas,
-                               const LaunchCfg& cfg, cudaStream_t s);
-cudaError_t launch_twoshot_ws8(bool allgather, const CollParams& p, DType dtype, DType wire, int ctas,
-                               const LaunchCfg& cfg, cudaStream_t s);
+// Reducing kernels (one-shot, two-shot, reduce_scatter): one translation unit per world-size class.
+enum ReduceKind : int { kOneShot = 0, kTwoShot = 1, kReduceScatter = 2 };
+cudaError_t launch_reduce_ws2(int kind, const CollParams& p, DType dtype, DType wire, int ctas,
+                              const LaunchCfg& cfg, cudaStream_t s);
+cudaError_t launch_reduce_ws4(int kind, const CollParams& p, DType dtype, DType wire, int ctas,
+                              const LaunchCfg& cfg, cudaStream_t s);
+cudaError_t launch_reduce_ws8(int kind, const CollParams& p, DType dtype, DType wire, int ctas,
+                              const LaunchCfg& cfg, cudaStream_t s);
 
 namespace {
 
-cudaError_t launch_twoshot(bool allgather, const CollParams& p, DType dtype, DType wire, int ctas,
-                           const LaunchCfg& cfg, cudaStream_t s) {
+cudaError_t launch_reduce(int kind, const CollParams& p, DType dtype, DType wire, int ctas,
+                          const LaunchCfg& cfg, cudaStream_t s) {
   const int ws = p.ctx[0].ws;
-  if (ws == 2) return launch_twoshot_ws2(allgather, p, dtype, wire, ctas, cfg, s);
-  if (ws <= 4) return launch_twoshot_ws4(allgather, p, dtype, wire, ctas, cfg, s);
-  return launch_twoshot_ws8(allgather, p, dtype, wire, ctas, cfg, s);
-}
-
-// ---------------------------------------------------------------------------
-// One-shot allreduce: every rank pushes its whole vector into slot[rank] of
-// every peer, then reduces the ws slots locally.
-// ---------------------------------------------------------------------------
-template <typename T, typename W, int OP>
-__device__ __forceinline__ void oneshot_reduce_phase(const CtaCtx& k, int64_t units, size_t slot_bytes,
-                                                     char* local_buf) {
-  using U = Unit<T, W>;
-  using Acc = typename U::Acc;
-  const RankCtx& c = *k.c;
-  const T* in = static_cast<const T*>(c.in);
-  T* out = static_cast<T*>(c.out);
-  const int64_t n = k.p->count;
-  const bool in_al = is_aligned16(in), out_al = is_aligned16(out);
-  const int64_t stride = static_cast<int64_t>(k.nctas) * k.nthreads;
-  for (int64_t u = static_cast<int64_t>(k.cta) * k.nthreads + k.tid; u < units; u += stride) {
-    Acc acc[U::N], x[U::N];
-    uint4 raw[kMaxWorld];
-#pragma unroll
-    for (int r = 0; r < kMaxWorld; ++r)
-      if (r < c.ws && r != c.rank) raw[r] = ldg16(local_buf + r * slot_bytes + u * 16);
-#pragma unroll
-    for (int r = 0; r < kMaxWorld; ++r) {
-      if (r >= c.ws) break;
-      if (r == c.rank) {
-        U::load_T(in, u * U::N, n, in_al, x);
-        U::round_through_wire(x);
-      } else {
-        U::unpack_W(raw[r], x);
-      }
-      if (r == 0) {
-#pragma unroll
-        for (int j = 0; j < U::N; ++j) acc[j] = x[j];
-      } else {
-        combine<T, OP>(acc, x, U::N);
-      }
-    }
-    if (OP == AVG || k.p->scale != 1.0f) {
-#pragma unroll
-      for (int j = 0; j < U::N; ++j) acc[j] = Traits<T>::scale(acc[j], k.p->scale);
-    }
-    U::store_T(out, u * U::N, n, out_al, acc);
-  }
-}
-
-template <typename T, typename W>
-__global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const __grid_constant__ CollParams p) {
-  using U = Unit<T, W>;
-  using Acc = typename U::Acc;
-  CtaCtx k = make_ctx(p);
-  const RankCtx& c = *k.c;
-  if (!enter_collective(k)) return;
-
-  const int64_t n = p.count;
-  const int64_t units = (n + U::N - 1) / U::N;
-  const size_t slot_bytes = round_up(static_cast<size_t>(units) * 16, 128);
-  const T* in = static_cast<const T*>(c.in);
-  const bool in_al = is_aligned16(in);
-  const int64_t stride = static_cast<int64_t>(k.nctas) * k.nthreads;
-  const int64_t first = static_cast<int64_t>(k.cta) * k.nthreads + k.tid;
-
-  // push
-  for (int64_t u0 = first; u0 < units; u0 += stride * kUnroll) {
-    uint4 v[kUnroll];
-#pragma unroll
-    for (int i = 0; i < kUnroll; ++i) {
-      int64_t u = u0 + i * stride;
-      if (u < units) {
-        Acc a[U::N];
-        U::load_T(in, u * U::N, n, in_al, a);
-        v[i] = U::pack_W(a);
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < kUnroll; ++i) {
-      int64_t u = u0 + i * stride;
-      if (u < units) {
-        for (int d = 1; d < c.ws; ++d) {
-          int q = c.rank + d;
-          if (q >= c.ws) q -= c.ws;
-          stg16(c.arena[q] + p.parity_offset + c.rank * slot_bytes + u * 16, v[i]);
-        }
-      }
-    }
-  }
-  signal_all(k, 0);
-  if (!wait_all(k, 0)) return;
-
-  char* local_buf = c.arena[c.rank] + p.parity_offset;
-  switch (p.op) {
-    case SUM: oneshot_reduce_phase<T, W, SUM>(k, units, slot_bytes, local_buf); break;
-    case AVG: oneshot_reduce_phase<T, W, AVG>(k, units, slot_bytes, local_buf); break;
-    case MIN: oneshot_reduce_phase<T, W, MIN>(k, units, slot_bytes, local_buf); break;
-    case MAX: oneshot_reduce_phase<T, W, MAX>(k, units, slot_bytes, local_buf); break;
-    default: oneshot_reduce_phase<T, W, PRODUCT>(k, units, slot_bytes, local_buf); break;
-  }
+  if (ws == 2) return launch_reduce_ws2(kind, p, dtype, wire, ctas, cfg, s);
+  if (ws <= 4) return launch_reduce_ws4(kind, p, dtype, wire, ctas, cfg, s);
+  return launch_reduce_ws8(kind, p, dtype, wire, ctas, cfg, s);
 }
 
 // ---------------------------------------------------------------------------
@@ -263,12 +166,6 @@ __global__ void __launch_bounds__(128) barrier_kernel(const __grid_constant__ Co
   wait_all(k, 0);
 }
 
-template <typename T, typename W> struct OneShotL {
-  static cudaError_t go(const CollParams& p, int ctas, const LaunchCfg& cfg, cudaStream_t s) {
-    return do_launch(allreduce_oneshot_kernel<T, W>, p, ctas, cfg.threads, cfg.emulate_ranks, s);
-  }
-};
-
 }  // namespace
 
 int pick_ctas(size_t bytes, int ws, int requested) {
@@ -296,18 +193,18 @@ size_t twoshot_arena_bytes(size_t nbytes_wire, int ws, bool push_gather) {
 cudaError_t launch_allreduce_oneshot(const CollParams& p, DType dtype, DType wire, LaunchCfg cfg,
                                      cudaStream_t s) {
   int ctas = clamp_ctas(cfg.ctas > 0 ? cfg.ctas : pick_ctas(p.count * dtype_size(wire) * (p.ctx[0].ws - 1), p.ctx[0].ws, 0), cfg);
-  return dispatch_types<OneShotL>(dtype, wire, p, ctas, cfg, s);
+  return launch_reduce(kOneShot, p, dtype, wire, ctas, cfg, s);
 }
 cudaError_t launch_allreduce_twoshot(const CollParams& p, DType dtype, DType wire, LaunchCfg cfg,
                                      cudaStream_t s) {
   int ctas = clamp_ctas(cfg.ctas > 0 ? cfg.ctas : pick_ctas(p.count * dtype_size(wire), p.ctx[0].ws, 0), cfg);
-  return launch_twoshot(true, p, dtype, wire, ctas, cfg, s);
+  return launch_reduce(kTwoShot, p, dtype, wire, ctas, cfg, s);
 }
 cudaError_t launch_reduce_scatter(const CollParams& p, DType dtype, DType wire, LaunchCfg cfg,
                                   cudaStream_t s) {
   int ctas = clamp_ctas(
       cfg.ctas > 0 ? cfg.ctas : pick_ctas(p.count * dtype_size(wire) * p.ctx[0].ws, p.ctx[0].ws, 0), cfg);
-  return launch_twoshot(false, p, dtype, wire, ctas, cfg, s);
+  return launch_reduce(kReduceScatter, p, dtype, wire, ctas, cfg, s);
 }
 cudaError_t launch_allgather(const CollParams& p, LaunchCfg cfg, cudaStream_t s) {
   int ctas = clamp_ctas(cfg.ctas > 0 ? cfg.ctas : pick_ctas(p.count * p.ctx[0].ws, p.ctx[0].ws, 0), cfg);

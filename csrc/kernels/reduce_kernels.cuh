@@ -1,4 +1,5 @@
-// Two-shot allreduce / reduce_scatter kernel template and its per-class launcher.
+// Reducing collective kernels (one-shot allreduce, two-shot allreduce, reduce_scatter) as
+// templates over the world-size class, and their per-class launcher.
 #pragma once
 
 #include "kernels/coll_common.cuh"
@@ -331,7 +332,67 @@ __global__ void __launch_bounds__(512) twoshot_kernel(const __grid_constant__ Co
 }
 
 
-template <int CLS> struct TwoShotClass {
+// ---------------------------------------------------------------------------
+// One-shot allreduce: every rank pushes its whole vector into slot[rank] of
+// every peer, then reduces the ws slots locally (same rank order, same
+// instruction sequence on every rank: bit-identical results).  CTA b owns the
+// contiguous unit range [b * per, (b + 1) * per) in both phases, so it only
+// waits for CTA b of its peers.
+// ---------------------------------------------------------------------------
+template <typename T, typename W, bool kSum, int CLS>
+__global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const __grid_constant__ CollParams p) {
+  using U = Unit<T, W>;
+  using Acc = typename U::Acc;
+  CtaCtx k = make_ctx(p);
+  const RankCtx& c = *k.c;
+  if (!enter_collective(k)) return;
+
+  const int64_t n = p.count;
+  const int64_t units = (n + U::N - 1) / U::N;
+  const size_t slot_bytes = round_up(static_cast<size_t>(units) * 16, 128);
+  const T* in = static_cast<const T*>(c.in);
+  const bool in_al = is_aligned16(in);
+  const int64_t per = (units + k.nctas - 1) / k.nctas;
+  const int64_t u0 = static_cast<int64_t>(k.cta) * per;
+  const int64_t u1 = u0 + per < units ? u0 + per : units;
+
+  // push
+  for (int64_t ub = u0; ub < u1; ub += static_cast<int64_t>(k.nthreads) * kUnroll) {
+    uint4 v[kUnroll];
+#pragma unroll
+    for (int i = 0; i < kUnroll; ++i) {
+      const int64_t u = ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
+      if (u < u1) {
+        if (U::kSame && in_al && (u + 1) * U::N <= n) {
+          v[i] = ldg16(in + u * U::N);
+        } else {
+          Acc a[U::N];
+          U::load_T(in, u * U::N, n, in_al, a);
+          v[i] = U::pack_W(a);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kUnroll; ++i) {
+      const int64_t u = ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
+      if (u < u1) {
+        for (int d = 1; d < c.ws; ++d) {
+          int q = c.rank + d;
+          if (q >= c.ws) q -= c.ws;
+          stg16(c.arena[q] + p.parity_offset + c.rank * slot_bytes + u * 16, v[i]);
+        }
+      }
+    }
+  }
+  signal_all(k, 0);
+  if (!wait_all(k, 0)) return;
+
+  char* local_buf = c.arena[c.rank] + p.parity_offset;
+  if (u0 < u1)
+    reduce_tile<T, W, kSum ? SUM : kRuntimeOp, CLS>(k, in, n, static_cast<T*>(c.out), u0, u1, slot_bytes, local_buf, false);
+}
+
+template <int CLS> struct ReduceClass {
   template <typename T, typename W> struct AllReduce {
     static cudaError_t go(const CollParams& p, int ctas, const LaunchCfg& cfg, cudaStream_t s) {
       if (p.op == SUM || p.op == AVG)
@@ -348,10 +409,20 @@ template <int CLS> struct TwoShotClass {
       return do_launch(twoshot_kernel<T, T, false, false, CLS>, p, ctas, cfg.threads, cfg.emulate_ranks, s);
     }
   };
-  static cudaError_t launch(bool allgather, const CollParams& p, DType dtype, DType wire, int ctas,
+  template <typename T, typename W> struct OneShot {
+    static cudaError_t go(const CollParams& p, int ctas, const LaunchCfg& cfg, cudaStream_t s) {
+      if (p.op == SUM || p.op == AVG)
+        return do_launch(allreduce_oneshot_kernel<T, W, true, CLS>, p, ctas, cfg.threads, cfg.emulate_ranks, s);
+      if (!std::is_same<T, W>::value) return cudaErrorInvalidValue;
+      return do_launch(allreduce_oneshot_kernel<T, T, false, CLS>, p, ctas, cfg.threads, cfg.emulate_ranks, s);
+    }
+  };
+  // kind: 0 one-shot allreduce, 1 two-shot allreduce, 2 reduce_scatter
+  static cudaError_t launch(int kind, const CollParams& p, DType dtype, DType wire, int ctas,
                             const LaunchCfg& cfg, cudaStream_t s) {
-    return allgather ? dispatch_types<AllReduce>(dtype, wire, p, ctas, cfg, s)
-                     : dispatch_types<ReduceScatter>(dtype, wire, p, ctas, cfg, s);
+    if (kind == 0) return dispatch_types<OneShot>(dtype, wire, p, ctas, cfg, s);
+    if (kind == 1) return dispatch_types<AllReduce>(dtype, wire, p, ctas, cfg, s);
+    return dispatch_types<ReduceScatter>(dtype, wire, p, ctas, cfg, s);
   }
 };
 

@@ -39,9 +39,9 @@ CPP_SOURCES = [
 CUDA_SOURCES = [
     "kernels/ew.cu",
     "kernels/collectives.cu",
-    "kernels/twoshot_ws2.cu",
-    "kernels/twoshot_ws4.cu",
-    "kernels/twoshot_ws8.cu",
+    "kernels/reduce_ws2.cu",
+    "kernels/reduce_ws4.cu",
+    "kernels/reduce_ws8.cu",
     "kernels/topk.cu",
     "kernels/stft.cu",
     "kernels/adamw.cu",
