@@ -159,7 +159,7 @@ class ProcessGroupMCCL : public c10d::Backend {
   c10::intrusive_ptr<c10d::Work> staged_via_host(c10d::OpType op, std::vector<at::Tensor> cuda_tensors,
                                                  std::function<c10::intrusive_ptr<c10d::Work>(std::vector<at::Tensor>&)> fn,
                                                  bool copy_back);
-  void poll_device();  // watchdog hook: status block + event-timed metrics
+  void poll_device(bool must = false);  // watchdog hook: status block + event-timed metrics
   void drain_finished();
   void device_health_check();
 

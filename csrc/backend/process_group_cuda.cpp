@@ -182,9 +182,13 @@ void ProcessGroupMCCL::drain_finished() {
   }
 }
 
-void ProcessGroupMCCL::poll_device() {
-  std::unique_lock<std::mutex> g(cuda_mu_, std::try_to_lock);
-  if (!g.owns_lock() || !cuda_) return;
+void ProcessGroupMCCL::poll_device(bool must) {
+  // The watchdog polls opportunistically; a blocking wait must not miss a status that another
+  // thread is reading right now, so it queues behind that thread instead of giving up.
+  std::unique_lock<std::mutex> g(cuda_mu_, std::defer_lock);
+  if (must) g.lock();
+  else if (!g.try_lock()) return;
+  if (!cuda_) return;
   CudaState& cs = *cuda_;
   c10::cuda::OptionalCUDAGuard guard(cs.dev);
   // 1. finished collectives -> metrics + watchdog
@@ -212,7 +216,7 @@ void ProcessGroupMCCL::poll_device() {
 }
 
 void ProcessGroupMCCL::device_health_check() {
-  poll_device();
+  poll_device(/*must=*/true);
   if (poisoned_.load()) throw MCCLError("collective failed: " + poison_reason());
 }
 
