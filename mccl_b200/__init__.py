@@ -8,7 +8,7 @@ Importing the package registers the backend for CUDA and CPU tensors::
     model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank])
 
 CUDA collectives are single fused sm_100a kernels that read and write the
-peers' memory over NVLink 5 / NVSwitch (see ``csrc/kernels/collectives.cu``);
+peers' memory over NVLink 5 / NVSwitch (see ``csrc/kernels/reduce_kernels.cuh`` and ``csrc/kernels/collectives.cu``);
 CPU collectives run over a framed TCP mesh.  The public names mirror the
 reference package (``mccl/__init__.py:167-179``): ``init``, ``get_config``,
 ``get_metrics``, ``log_metrics``, ``reset_metrics``, ``trim_staging_pool``,
