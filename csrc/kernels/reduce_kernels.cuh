@@ -22,9 +22,6 @@ namespace {
 // that needs twice the arena space.
 // For reduce_scatter the "chunks" are the ws equal parts of the input list.
 // ---------------------------------------------------------------------------
-// Reduces units [u0, u1) of the chunk this rank owns.  G units are in flight per
-// thread so that G * ws independent 16-byte loads are outstanding: with few
-// ranks one unit per thread would leave HBM idle.
 // Stores one reduced unit: wire-rounded copy for the peers (pushed to them, or kept in
 // slot[owner] for them to pull) and the owner's own output.
 template <typename T, typename W>
