@@ -664,7 +664,8 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::allreduce_scaled(std::vector<at
     if (scale != 1.0f) t.mul_(scale);
     return completed_work(c10d::OpType::ALLREDUCE, {t}, &t);
   }
-  if (t.is_cuda()) return cuda_allreduce(t, c10d::ReduceOp::SUM, scale);
+  // gradient buckets from a DDP hook: they overlap the rest of backward
+  if (t.is_cuda()) return cuda_allreduce(t, c10d::ReduceOp::SUM, scale, nullptr, /*overlapped=*/true);
   ensure_transport();
   at::Tensor tt = t;
   return submit_host(c10d::OpType::ALLREDUCE, "mccl:all_reduce_scaled", t.nbytes(), {t},
@@ -685,7 +686,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::allreduce_scaled_then(std::vect
     if (epilogue) epilogue(c10::cuda::getCurrentCUDAStream(t.device().index()).stream());
     return completed_work(c10d::OpType::ALLREDUCE, {t}, &t);
   }
-  return cuda_allreduce(t, c10d::ReduceOp::SUM, scale, std::move(epilogue));
+  return cuda_allreduce(t, c10d::ReduceOp::SUM, scale, std::move(epilogue), /*overlapped=*/true);
 }
 
 c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::allreduce_coalesced(

@@ -149,7 +149,8 @@ class ProcessGroupMCCL : public c10d::Backend {
   // ---- CUDA path (process_group_cuda.cpp) ----------------------------------
   void ensure_cuda(c10::DeviceIndex dev);
   c10::intrusive_ptr<c10d::Work> cuda_allreduce(at::Tensor& t, c10d::ReduceOp::RedOpType op, float prescale,
-                                                std::function<void(cudaStream_t)> epilogue = nullptr);
+                                                std::function<void(cudaStream_t)> epilogue = nullptr,
+                                                bool overlapped = false);
   c10::intrusive_ptr<c10d::Work> cuda_broadcast(at::Tensor& t, int root);
   c10::intrusive_ptr<c10d::Work> cuda_allgather(at::Tensor& out_flat, const at::Tensor& in,
                                                 std::vector<at::Tensor>* scatter_to);

@@ -351,9 +351,9 @@ struct CudaPath {
       }
   }
 
-  kern::LaunchCfg cfg(size_t bytes) {
+  kern::LaunchCfg cfg(size_t bytes, bool overlapped = false) {
     kern::LaunchCfg c;
-    c.ctas = pg.tuner_.ctas_for(cs.arena->world_size(), bytes, static_cast<int>(pg.options_->comm_ctas));
+    c.ctas = pg.tuner_.ctas_for(cs.arena->world_size(), bytes, static_cast<int>(pg.options_->comm_ctas), overlapped);
     return c;
   }
 
@@ -414,7 +414,8 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::staged_via_host(
 
 c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allreduce(at::Tensor& t, c10d::ReduceOp::RedOpType op,
                                                                 float prescale,
-                                                                std::function<void(cudaStream_t)> epilogue) {
+                                                                std::function<void(cudaStream_t)> epilogue,
+                                                                bool overlapped) {
   const auto dev = t.device().index();
   ensure_cuda(dev);
   if (!cuda_->p2p) {
@@ -471,9 +472,9 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allreduce(at::Tensor& t, c
     p.scale = (op == c10d::ReduceOp::AVG ? 1.0f / ws : 1.0f) * prescale;
     if (!cp.skip) {
       if (v == Variant::ONESHOT)
-        MCCL_LAUNCH_CHECK(kern::launch_allreduce_oneshot(p, dt, wire, cp.cfg(wire_bytes * (ws - 1)), cp.stream.stream()));
+        MCCL_LAUNCH_CHECK(kern::launch_allreduce_oneshot(p, dt, wire, cp.cfg(wire_bytes * (ws - 1), overlapped), cp.stream.stream()));
       else
-        MCCL_LAUNCH_CHECK(kern::launch_allreduce_twoshot(p, dt, wire, cp.cfg(wire_bytes), cp.stream.stream()));
+        MCCL_LAUNCH_CHECK(kern::launch_allreduce_twoshot(p, dt, wire, cp.cfg(wire_bytes, overlapped), cp.stream.stream()));
     }
     sent += v == Variant::ONESHOT ? wire_bytes * (ws - 1) : 2 * wire_bytes * (ws - 1) / ws;
     MCCL_DEBUG("allreduce seq=%u epoch=%u %s bytes=%zu wire=%d", cp.seq, p.seq,

@@ -52,7 +52,7 @@ def test_tuner_file_overrides(native, tmp_path, monkeypatch):
     import json
     f = tmp_path / "tune.json"
     f.write_text(json.dumps({"ws8_oneshot_max_bytes": 524288, "ws8_ctas_large": 48, "segment_bytes": 33554432,
-                             "ws8_push_gather": 1, "ws2_push_gather": 0,
+                             "ws8_push_gather": 1, "ws2_push_gather": 0, "ws8_ctas_overlap": 40,
                              "measured": [{"bytes": 1, "oneshot_us": 2.0}]}))
     monkeypatch.setenv("MCCL_TUNE_FILE", str(f))
     pg = native._create_process_group(dist.HashStore(), 0, 1, datetime.timedelta(seconds=10))
@@ -60,6 +60,7 @@ def test_tuner_file_overrides(native, tmp_path, monkeypatch):
     assert t["ws8_oneshot_max_bytes"] == 524288 and t["ws8_ctas_large"] == 48 and t["segment_bytes"] == 33554432
     assert t["ws2_oneshot_max_bytes"] == 16 << 20   # untouched default
     assert t["ws8_push_gather"] == 1 and t["ws2_push_gather"] == 0 and t["ws4_push_gather"] == 0
+    assert t["ws8_ctas_overlap"] == 40 and t["ws2_ctas_overlap"] == 32 and t["ws4_ctas_overlap"] == 0
     pg.shutdown()
 
 
