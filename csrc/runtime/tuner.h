@@ -33,15 +33,17 @@ class Tuner {
       // one-shot moves (ws-1)*N per GPU instead of 2*(ws-1)/ws*N: its advantage
       // (one flag round instead of two) holds up to a few hundred KiB.
       // Measured crossovers (fp32, back-to-back calls): with 2 ranks both variants move N per
-      // direction, so the single flag round of one-shot wins up to 16 MiB (beyond that its extra HBM pass costs more).
-      oneshot_max_[ws] = ws <= 2 ? (size_t(16) << 20) : ws <= 4 ? (size_t(4) << 20) : (size_t(1) << 20);
+      // direction, so the single flag round of one-shot wins up to 32 MiB (85 us vs 89 us; at 64 MiB
+      // its extra HBM pass costs more: 160 us vs 153 us).
+      oneshot_max_[ws] = ws <= 2 ? (size_t(32) << 20) : ws <= 4 ? (size_t(4) << 20) : (size_t(1) << 20);
       ctas_small_[ws] = 32;
       ctas_large_[ws] = 64;  // two lanes may run at once: 2 x 64 CTAs stay below the 148 SMs
       // measured on 2 ranks: 64 MiB 158 us pushed vs 185 us pulled (the stores overlap the reduction)
       push_gather_[ws] = ws <= 2 ? 1 : 0;
       // Gradient buckets run while backward GEMMs need the SMs.  Measured on 2 ranks (94 M MLP, DDP):
-      // 71.1 k samples/s with 32 CTAs per allreduce, 66.6 k with 64, 67.3 k with 16.  0 = same as ctas_large.
-      ctas_overlap_[ws] = ws <= 2 ? 32 : 0;
+      // 73.7 k samples/s with 48 CTAs per allreduce, 71.1 k with 32, 71.2 k with 24, 67.3 k with 16,
+      // 66.6 k with 64.  0 = same as ctas_large.
+      ctas_overlap_[ws] = ws <= 2 ? 48 : 0;
     }
   }
 

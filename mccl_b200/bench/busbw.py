@@ -91,7 +91,7 @@ def tune(path, rank, ws, dev):
 
     Two extra process groups are created with the variant pinned through ``MCCLOptions``
     (``pg_options`` are honoured by the backend); fp32 allreduce is timed from 16 KiB to
-    16 MiB and the largest size at which one-shot is at least as fast becomes
+    64 MiB and the largest size at which one-shot is at least as fast becomes
     ``ws<N>_oneshot_max_bytes``.  The two forms of the two-shot second half (peers pull the
     reduced chunks / owners push them) are then timed at 32 and 64 MiB; ``ws<N>_push_gather``
     is 1 when pushing wins at both.  Load the result with ``MCCL_TUNE_FILE`` on every rank.
@@ -105,7 +105,7 @@ def tune(path, rank, ws, dev):
         o.algo = algo
         groups[algo] = dist.new_group(backend="mccl", pg_options=o)
     best, rows, size = 0, [], 16 << 10
-    while size <= (16 << 20):
+    while size <= (64 << 20):
         numel = size // 4
         t = {}
         for algo, g in groups.items():
