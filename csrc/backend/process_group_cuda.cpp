@@ -602,42 +602,27 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_reduce_scatter(at::Tensor&
   const kern::DType dt = to_kern_dtype(out.scalar_type());
   const size_t esz = out.element_size();
   const int64_t n = out.numel();
-  CudaPath cp(*this, c10d::OpType::REDUCE_SCATTER, "mccl:reduce_scatter", in_flat.nbytes(), {out}, dev, /*serial=*/true);
+  CudaPath cp(*this, c10d::OpType::REDUCE_SCATTER, "mccl:reduce_scatter", in_flat.nbytes(), {out}, dev);
   cp.keep(in_flat);
   cp.keep(out);
   const size_t cap = cuda_->arena->parity_bytes();
-  // slot = one chunk slice; ws slots per parity buffer
-  int64_t seg_elems = static_cast<int64_t>((cap / ws) / esz) / 256 * 256;
+  // slot = one chunk slice; ws slots per parity buffer.  Chunks larger than a slot go in slices:
+  // launch i reduces elements [off, off + cnt) of every chunk, reading them in place (chunk q
+  // starts at in + q * n: the kernel's chunk pitch), and consecutive launches alternate lanes.
+  int64_t seg_elems = static_cast<int64_t>(std::min(tuner_.segment_bytes(), cap) / ws / esz) / 256 * 256;
   seg_elems = std::max<int64_t>(seg_elems, 256);
   const char* ibase = static_cast<const char*>(in_flat.data_ptr());
   char* obase = static_cast<char*>(out.data_ptr());
-  if (n <= seg_elems) {
+  for (int64_t off = 0; off < n; off += seg_elems) {
+    const int64_t cnt = std::min(seg_elems, n - off);
     kern::CollParams p = cp.params();
-    p.ctx[0].in = ibase;
-    p.ctx[0].out = obase;
-    p.count = n;
+    p.ctx[0].in = ibase + off * esz;
+    p.ctx[0].out = obase + off * esz;
+    p.count = cnt;
+    p.chunk_pitch = n;
     p.op = to_kern_op(op);
     p.scale = op == c10d::ReduceOp::AVG ? 1.0f / ws : 1.0f;
-    if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_reduce_scatter(p, dt, dt, cp.cfg(in_flat.nbytes()), cp.stream.stream()));
-  } else {
-    // Chunks larger than a slot: the kernel wants chunk q at in + q*count, so
-    // pack each slice of all ws chunks contiguously first.
-    c10::cuda::CUDAStreamGuard sg(cp.stream);
-    at::Tensor tmp = at::empty({static_cast<int64_t>(ws) * seg_elems}, out.options());
-    for (int64_t off = 0; off < n; off += seg_elems) {
-      const int64_t cnt = std::min(seg_elems, n - off);
-      for (int r = 0; r < ws; ++r)
-        MCCL_CUDA_CHECK(cudaMemcpyAsync(static_cast<char*>(tmp.data_ptr()) + r * cnt * esz,
-                                        ibase + (static_cast<int64_t>(r) * n + off) * esz, cnt * esz,
-                                        cudaMemcpyDeviceToDevice, cp.stream.stream()));
-      kern::CollParams p = cp.params();
-      p.ctx[0].in = tmp.data_ptr();
-      p.ctx[0].out = obase + off * esz;
-      p.count = cnt;
-      p.op = to_kern_op(op);
-      p.scale = op == c10d::ReduceOp::AVG ? 1.0f / ws : 1.0f;
-      if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_reduce_scatter(p, dt, dt, cp.cfg(cnt * esz * ws), cp.stream.stream()));
-    }
+    if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_reduce_scatter(p, dt, dt, cp.cfg(cnt * esz * ws), cp.stream.stream()));
   }
   metrics_.record_transport_bytes(out.nbytes() * (ws - 1), out.nbytes() * (ws - 1));
   return cp.finish();

@@ -171,11 +171,14 @@ class EmuGroup {
       CK(kern::launch_allreduce_twoshot(p, dt, wd, cfg(ctas), at::cuda::getCurrentCUDAStream()));
     }
   }
-  void reduce_scatter(std::vector<at::Tensor> outs, std::vector<at::Tensor> ins, const std::string& op, int ctas) {
+  // pitch > 0: chunk q of the input starts at element q * pitch (a slice of a larger input)
+  void reduce_scatter(std::vector<at::Tensor> outs, std::vector<at::Tensor> ins, const std::string& op, int ctas,
+                      int64_t pitch) {
     c10::cuda::CUDAGuard g(ins[0].device());
     kern::DType dt = to_kern_dtype(ins[0].scalar_type());
     kern::CollParams p = params(ins, outs);
     p.count = outs[0].numel();
+    p.chunk_pitch = pitch;
     p.op = parse_op(op);
     p.scale = p.op == kern::AVG ? 1.0f / ws_ : 1.0f;
     check_fits(kern::twoshot_arena_bytes(static_cast<size_t>(p.count) * ws_ * kern::dtype_size(dt), ws_) + 128 * ws_);
@@ -696,7 +699,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("algo") = "oneshot", py::arg("wire") = "none", py::arg("scale") = 1.0, py::arg("ctas") = 0,
            py::arg("tiles") = 1, py::arg("push_gather") = false)
       .def("reduce_scatter", &EmuGroup::reduce_scatter, py::arg("outputs"), py::arg("inputs"),
-           py::arg("op") = "sum", py::arg("ctas") = 0)
+           py::arg("op") = "sum", py::arg("ctas") = 0, py::arg("pitch") = 0)
       .def("allgather", &EmuGroup::allgather, py::arg("outputs"), py::arg("inputs"), py::arg("ctas") = 0)
       .def("broadcast", &EmuGroup::broadcast, py::arg("tensors"), py::arg("root"), py::arg("ctas") = 0)
       .def("barrier", &EmuGroup::barrier)

@@ -77,6 +77,7 @@ struct CollParams {
   float scale;             // multiplied into the result (1/world for AVG, DDP pre-division...)
   unsigned long long wait_ns;  // bound on every in-kernel wait
   int tiles;               // two-shot: pipeline tiles per CTA (<=1: bulk phases)
+  int64_t chunk_pitch;     // reduce_scatter: elements between the starts of consecutive input chunks (0: count)
   int push_gather;         // two-shot allreduce: owners push reduced chunks (needs 2x arena) instead of peers pulling
 };
 

@@ -237,7 +237,10 @@ __global__ void __launch_bounds__(512) twoshot_kernel(const __grid_constant__ Co
     return e < chunk_units ? e : chunk_units;
   };
   char* local_buf = c.arena[c.rank] + p.parity_offset;
-  const T* in_chunk = in + static_cast<int64_t>(c.rank) * chunk_elems;
+  // distance between the starts of consecutive input chunks (reduce_scatter may read a slice of
+  // every chunk of a larger input: pitch > count)
+  const int64_t in_pitch = (!kAllGather && p.chunk_pitch > 0) ? p.chunk_pitch : chunk_elems;
+  const T* in_chunk = in + static_cast<int64_t>(c.rank) * in_pitch;
   const int64_t own_n = chunk_len(c.rank);
   T* out_chunk = kAllGather ? out + static_cast<int64_t>(c.rank) * chunk_elems : out;
   const int last_stage = kAllGather ? 2 : 1;
@@ -249,7 +252,7 @@ __global__ void __launch_bounds__(512) twoshot_kernel(const __grid_constant__ Co
       for (int d = 1; d < c.ws; ++d) {
         int q = c.rank + d;
         if (q >= c.ws) q -= c.ws;
-        const T* src = in + static_cast<int64_t>(q) * chunk_elems;
+        const T* src = in + static_cast<int64_t>(q) * in_pitch;
         const int64_t src_n = chunk_len(q);
         const bool al = is_aligned16(src);
         char* dst = c.arena[q] + p.parity_offset + c.rank * slot_bytes;

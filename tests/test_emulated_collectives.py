@@ -269,3 +269,20 @@ def test_twoshot_push_gather_needs_twice_the_arena(native, cuda_device):
     with pytest.raises(Exception, match="arena bytes"):
         g.allreduce(xs, "sum", "twoshot", "none", 1.0, 4, 1, True)
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("ws", [2, 3, 8])
+def test_reduce_scatter_reads_slices_in_place(native, cuda_device, ws):
+    # a chunk pitch larger than the count: each launch reduces one slice of every chunk of a larger
+    # input without packing it first (how inputs beyond one arena buffer are handled)
+    g = native.EmuGroup(ws, 16 << 20)
+    n, cnt = 5 * 256 + 77, 512          # per-rank chunk length, slice length
+    ins = [torch.randn(ws * n, generator=torch.Generator().manual_seed(r)).to(cuda_device) for r in range(ws)]
+    want = torch.stack([x.double() for x in ins]).sum(0)
+    outs = [torch.zeros(n, device=cuda_device) for _ in range(ws)]
+    for off in range(0, n, cnt):
+        c = min(cnt, n - off)
+        g.reduce_scatter([o[off:off + c] for o in outs], [x[off:] for x in ins], "sum", 4, n)
+    torch.cuda.synchronize()
+    for r in range(ws):
+        assert torch.allclose(outs[r].double(), want[r * n:(r + 1) * n], rtol=1e-5, atol=1e-5)
