@@ -440,8 +440,12 @@ void ProcessGroupMCCL::cpu_allreduce(uint32_t seq, at::Tensor& t, c10d::ReduceOp
         if (r != me) transport_->wait_recv(tk[r]);
     }
     PhaseTimer pt{metrics_, seq, Metrics::Phase::REDUCE};
-    // Fixed rank order: acc = x0 op x1 op ... ; `data` holds x_me.
-    if (me != 0) {
+    // Fixed rank order: acc = x0 op x1 op ... ; `data` holds x_me.  With two ranks the
+    // operation is a single commutative elementwise op (IEEE add/mul/min/max give the same
+    // bits for either operand order), so both ranks reduce in place without the reordering copies.
+    if (ws == 2) {
+      cpu_reduce_into(data, bufs[1 - me].data(), n, dtype, op);
+    } else if (me != 0) {
       PooledBuffer mine = pool.acquire(nbytes);
       std::memcpy(mine.data(), data, nbytes);
       std::memcpy(data, bufs[0].data(), nbytes);
