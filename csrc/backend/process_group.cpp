@@ -424,6 +424,42 @@ void ProcessGroupMCCL::cpu_allreduce(uint32_t seq, at::Tensor& t, c10d::ReduceOp
     return;
   }
 
+  constexpr size_t kPairSegment = size_t(2) << 20;
+  if (ws == 2 && nbytes >= 2 * kPairSegment) {
+    // Two ranks, large message: exchange in segments and reduce segment i-1 while segment i is on
+    // the wire (both directions run at the same rate, so it has arrived by then).  Same bytes as the
+    // plain exchange, but the reduction no longer follows the transfer.
+    const int peer = 1 - me;
+    const int64_t seg_elems = static_cast<int64_t>(kPairSegment / esz);
+    const int nseg = static_cast<int>((n + seg_elems - 1) / seg_elems);
+    PooledBuffer theirs = pool.acquire(nbytes);
+    std::vector<HostTransport::TicketPtr> tk(nseg);
+    auto seg_len = [&](int i) { return std::min<int64_t>(seg_elems, n - static_cast<int64_t>(i) * seg_elems); };
+    for (int i = 0; i < nseg; ++i)
+      tk[i] = transport_->post_recv(peer, HostTransport::collective_key(seq, 16 + i),
+                                    theirs.data() + static_cast<size_t>(i) * seg_elems * esz, seg_len(i) * esz);
+    auto finish_seg = [&](int i) {
+      {
+        PhaseTimer pt{metrics_, seq, Metrics::Phase::NETWORK};
+        transport_->wait_recv(tk[i]);
+      }
+      PhaseTimer pt{metrics_, seq, Metrics::Phase::REDUCE};
+      uint8_t* d = data + static_cast<size_t>(i) * seg_elems * esz;
+      cpu_reduce_into(d, theirs.data() + static_cast<size_t>(i) * seg_elems * esz, seg_len(i), dtype, op);
+      if (op == c10d::ReduceOp::AVG) cpu_scale_inplace(d, seg_len(i), dtype, 0.5);
+    };
+    for (int i = 0; i < nseg; ++i) {
+      {
+        PhaseTimer pt{metrics_, seq, Metrics::Phase::NETWORK};
+        transport_->send(peer, wop, seq, 16 + i, data + static_cast<size_t>(i) * seg_elems * esz, seg_len(i) * esz);
+      }
+      if (i >= 1) finish_seg(i - 1);  // segment i-1 of `data` has been sent: safe to overwrite
+    }
+    finish_seg(nseg - 1);
+    metrics_.record_transport_bytes(nbytes, nbytes);
+    return;
+  }
+
   if (ws == 2 || nbytes <= static_cast<size_t>(options_->small_msg_threshold)) {
     // All-exchange: (ws-1)*N on the wire per rank, one round.
     std::vector<PooledBuffer> bufs(ws);

@@ -192,3 +192,30 @@ def _crc_and_small_chunks(rank, ws):
 def test_crc_and_chunked_frames():
     # 64 KiB frames force multi-chunk messages; CRC on every frame
     run_workers(_crc_and_small_chunks, 3, timeout=120, env={"MCCL_CHUNK_BYTES": "65536", "MCCL_TRANSPORT_CRC": "1"})
+
+
+def _pair_large(rank, ws):
+    import torch, torch.distributed as dist
+    # two ranks, >= 4 MiB: segmented exchange with the reduction overlapped (odd length: ragged last segment)
+    n = 3_000_001
+    g = torch.Generator().manual_seed(7 + rank)
+    x = torch.randn(n, generator=g)
+    both = [torch.empty_like(x) for _ in range(ws)]
+    dist.all_gather(both, x)
+    for op, want in ((dist.ReduceOp.SUM, both[0] + both[1]), (dist.ReduceOp.MAX, torch.maximum(both[0], both[1])),
+                     (dist.ReduceOp.AVG, (both[0] + both[1]) * 0.5)):
+        t = x.clone()
+        dist.all_reduce(t, op=op)
+        assert torch.equal(t, want), op
+    i = torch.arange(n, dtype=torch.int64) * (rank + 1)
+    dist.all_reduce(i)
+    assert torch.equal(i, torch.arange(n, dtype=torch.int64) * 3)
+    works = [dist.all_reduce(torch.full((1_500_000,), float(k)), async_op=True) for k in range(4)]
+    for w in works:
+        w.wait()
+    assert mccl.get_metrics().total_errors == 0
+
+
+@pytest.mark.parametrize("env", [{}, {"MCCL_CHUNK_BYTES": "65536", "MCCL_TRANSPORT_CRC": "1"}], ids=["defaults", "small-frames-crc"])
+def test_two_rank_large_allreduce_segmented(env):
+    run_workers(_pair_large, 2, timeout=240, env=env)
