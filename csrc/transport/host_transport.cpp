@@ -432,6 +432,8 @@ HostTransport::TicketPtr HostTransport::post_recv(int peer, uint64_t key, void* 
     return t;
   }
   p.posted[key].push_back(t);
+  lk.unlock();
+  p.cv.notify_all();  // a reader may be holding a large frame back for exactly this receive
   return t;
 }
 
@@ -531,6 +533,11 @@ void HostTransport::fail_all(const std::string& why) {
   }
 }
 
+namespace {
+constexpr size_t kParkGraceBytes = 256 << 10;
+constexpr int kParkGraceMs = 3;
+}  // namespace
+
 void HostTransport::route_payload(int peer, const MessageHeader& h) {
   Peer& p = *peers_[peer];
   const uint64_t key = key_of(h);
@@ -542,7 +549,7 @@ void HostTransport::route_payload(int peer, const MessageHeader& h) {
   uint8_t* dst = nullptr;
   {
     std::unique_lock<std::mutex> lk(p.mu);
-    bool waited_for_space = false;
+    bool waited_for_space = false, grace_done = false;
     for (;;) {
       // 1. continuation of a message that is already being parked
       auto pit = p.parked.find(key);
@@ -559,7 +566,18 @@ void HostTransport::route_payload(int peer, const MessageHeader& h) {
         if (it->second.empty()) p.posted.erase(it);
       }
       if (ticket) break;
-      // 3. park it.  Waiting for park space drops the lock, so a receive may be
+      // 3. no receive yet.  A large frame is worth a short grace period: in back-to-back
+      // collectives the sender runs a little ahead of the receiver's next post, and parking
+      // costs a pooled buffer plus a second copy of the whole payload.
+      if (!grace_done && n >= kParkGraceBytes) {
+        grace_done = true;
+        p.cv.wait_for(lk, std::chrono::milliseconds(kParkGraceMs), [&] {
+          auto q = p.posted.find(key);
+          return stopping_.load() || aborted_.load() || (q != p.posted.end() && !q->second.empty());
+        });
+        continue;
+      }
+      // 4. park it.  Waiting for park space drops the lock, so a receive may be
       // posted meanwhile: look again before creating the parked message.
       if (!waited_for_space) {
         lk.unlock();
