@@ -28,3 +28,12 @@ def test_ddp_dummy_train_two_cpu_ranks(tmp_path):
     r = _run(["examples/benchmark_throughput.py", str(base), str(stats), "--out", str(tmp_path / "bench")])
     assert r.returncode == 0 and "throughput ratio" in r.stdout, r.stderr[-1000:]
     assert (tmp_path / "bench.npz").exists()
+
+
+def test_shell_scripts_parse():
+    import glob, os, subprocess
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples")
+    scripts = sorted(glob.glob(os.path.join(root, "*.sh")))
+    assert len(scripts) >= 4
+    for s in scripts:
+        subprocess.run(["bash", "-n", s], check=True)
