@@ -89,6 +89,10 @@ _FIELD_SPEC: Dict[str, tuple] = {
     "device_wait_us": ("MCCL_DEVICE_WAIT_US", _in_range(1, None), "cuda"),
     "arena_bytes": ("MCCL_ARENA_BYTES", _in_range(1 << 20, None), "cuda"),
     "blocking_wait": ("MCCL_BLOCKING_WAIT", None, "cuda"),
+    "gather": ("MCCL_GATHER", _one_of("auto", "pull", "push"), "cuda"),
+    "tiles": ("MCCL_TILES", _in_range(1, 64), "cuda"),
+    "segment_bytes": ("MCCL_SEGMENT_BYTES", _in_range(1 << 20, None), "cuda"),
+    "device_timing": ("MCCL_DEVICE_TIMING", _in_range(0, None), "cuda"),
     # integration hint only (never exported)
     "ddp_bucket_mb": (None, _in_range(1, None), "both"),
 }
@@ -142,6 +146,10 @@ class MCCLConfig:
     device_wait_us: int = 60_000_000
     arena_bytes: int = 128 * 1024 * 1024
     blocking_wait: bool = False
+    gather: str = "auto"            # second half of the two-shot allreduce: tuner table | peers pull | owners push
+    tiles: int = 1                  # two-shot pipeline tiles per CTA
+    segment_bytes: int = 64 * 1024 * 1024   # large allreduces run as segments of this size on alternating lanes
+    device_timing: int = 8          # every Nth CUDA collective is device-timed for the metrics (0: never)
     # integration hint (not exported to the native layer)
     ddp_bucket_mb: int = 25
 
@@ -150,7 +158,8 @@ class MCCLConfig:
     # Fields whose default must not be exported unless the user set them: the
     # native default differs (ephemeral ports) or derives from other knobs.
     _EXPORT_ONLY_IF_CHANGED = ("port_base", "device_wait_us", "oneshot_max_bytes", "comm_ctas",
-                               "arena_bytes", "blocking_wait", "algo", "wire_dtype")
+                               "arena_bytes", "blocking_wait", "algo", "wire_dtype", "gather", "tiles", "segment_bytes",
+                               "device_timing")
 
     def __post_init__(self) -> None:
         self._ENV_MAP = {env: name for name, (env, _v, _s) in _FIELD_SPEC.items() if env}

@@ -106,3 +106,23 @@ def test_presets():
 def test_scope_annotations():
     assert MCCLConfig.scope("fast_math") == "compat" and MCCLConfig.scope("algo") == "cuda"
     assert MCCLConfig.scope("chunk_bytes") == "host"
+
+
+def test_data_plane_knobs_validate_and_export(monkeypatch):
+    import os
+    import mccl_b200 as mccl
+    for k in ("MCCL_GATHER", "MCCL_TILES", "MCCL_SEGMENT_BYTES", "MCCL_DEVICE_TIMING"):
+        monkeypatch.delenv(k, raising=False)
+    cfg = mccl.MCCLConfig()
+    cfg.to_env()
+    assert "MCCL_GATHER" not in os.environ and "MCCL_DEVICE_TIMING" not in os.environ   # defaults stay unexported
+    cfg = mccl.MCCLConfig(gather="push", tiles=2, segment_bytes=32 << 20, device_timing=0)
+    cfg.to_env()
+    assert os.environ["MCCL_GATHER"] == "push" and os.environ["MCCL_TILES"] == "2"
+    assert os.environ["MCCL_SEGMENT_BYTES"] == str(32 << 20) and os.environ["MCCL_DEVICE_TIMING"] == "0"
+    import pytest
+    for bad in (dict(gather="shove"), dict(tiles=0), dict(segment_bytes=1000), dict(device_timing=-1)):
+        with pytest.raises(ValueError):
+            mccl.MCCLConfig(**bad)
+    for k in ("MCCL_GATHER", "MCCL_TILES", "MCCL_SEGMENT_BYTES", "MCCL_DEVICE_TIMING"):
+        os.environ.pop(k, None)
