@@ -55,6 +55,14 @@ ProcessGroupMCCL::ProcessGroupMCCL(const c10::intrusive_ptr<c10d::Store>& store,
   if (std::getenv("MCCL_ALLREDUCE_ALGO"))
     MCCL_WARN("MCCL_ALLREDUCE_ALGO was removed: use MCCL_ALGO (auto|oneshot|twoshot|staged)");
 
+  if (options_->gather != "auto" && options_->gather != "pull" && options_->gather != "push") {
+    MCCL_WARN("MCCL_GATHER=%s is not one of auto|pull|push: using auto", options_->gather.c_str());
+    options_->gather = "auto";
+  }
+  if (options_->algo != "auto" && options_->algo != "oneshot" && options_->algo != "twoshot" && options_->algo != "staged") {
+    MCCL_WARN("MCCL_ALGO=%s is not one of auto|oneshot|twoshot|staged: using auto", options_->algo.c_str());
+    options_->algo = "auto";
+  }
   device_timing_ = static_cast<int>(std::max<int64_t>(0, env_int("MCCL_DEVICE_TIMING", 8)));
   profile_titles_ = env_bool("MCCL_PROFILE_TITLES", false);
   compressor_ = make_compressor(options_->compression, options_->topk_ratio);
@@ -115,7 +123,7 @@ ProcessGroupMCCL::~ProcessGroupMCCL() { shutdown(); }
 std::string ProcessGroupMCCL::describe() const {
   std::ostringstream o;
   o << "ProcessGroupMCCL rank " << getRank() << "/" << getSize() << " algo=" << options_->algo
-    << " overlap_comm=" << options_->overlap_comm << " arena=" << (options_->arena_bytes >> 20) << "MiB x2"
+    << " overlap_comm=" << options_->overlap_comm << " arena=" << (options_->arena_bytes >> 20) << "MiB x4"
     << " oneshot_max(ws)=" << tuner_.oneshot_max_bytes(std::min(getSize(), kern::kMaxWorld))
     << " segment=" << (tuner_.segment_bytes() >> 20) << "MiB"
     << " lanes=" << options_->lanes << " comm_ctas=" << options_->comm_ctas << " wire_dtype=" << options_->wire_dtype
