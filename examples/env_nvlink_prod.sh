@@ -7,3 +7,6 @@ export MCCL_WATCHDOG_TIMEOUT_MS=${MCCL_WATCHDOG_TIMEOUT_MS:-300000}
 export DDP_BUCKET_MB=${DDP_BUCKET_MB:-25}
 # export MCCL_WIRE_DTYPE=bf16                        # fp32 gradients travel as bf16 (fused cast)
 # export MCCL_COMPRESSION=topk MCCL_TOPK_RATIO=0.01  # top-k gradients with error feedback
+# export MCCL_TUNE_FILE=/path/to/tune.json           # written by: python -m mccl_b200.bench.busbw --tune FILE
+# export MCCL_GATHER=push                            # two-shot second half: owners push (default only at 2 ranks)
+# export MCCL_DEVICE_TIMING=0                        # no device-timed samples for the metrics (saves ~3 us per call)
