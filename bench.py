@@ -43,6 +43,8 @@ def parse_args():
     ap.add_argument("--bucket-mb", type=int, default=25)
     ap.add_argument("--no-fused-hook", action="store_true", help="stock DDP divide + SUM allreduce")
     ap.add_argument("--no-fused-optim", action="store_true", help="torch.optim.AdamW instead of the fused kernel")
+    ap.add_argument("--no-compare", action="store_true",
+                    help="skip the in-process comparison arms (mccl + torch AdamW, and torch's NCCL backend)")
     ap.add_argument("--optim-in-backward", default="off", choices=["on", "off"],
                     help="AdamW per bucket right behind its allreduce instead of one step after backward "
                          "(measured slower for this model: the per-bucket Python hook stalls the autograd thread)")
@@ -132,27 +134,6 @@ def main():
 
     from mccl_b200.models import MLP94M, num_parameters
 
-    torch.manual_seed(42)
-    model = MLP94M().to(dev)
-    n_params = num_parameters(model)
-    in_bw = False
-    if args.impl == "mccl":
-        from mccl_b200.parallel import wrap_ddp
-        from mccl_b200.optim import FusedAdamW
-        opt = (torch.optim.AdamW(model.parameters(), lr=1e-3, fused=True) if args.no_fused_optim
-               else FusedAdamW(model.parameters(), lr=1e-3))
-        want_bw = args.optim_in_backward == "on"
-        in_bw = want_bw and not (args.no_fused_optim or args.no_fused_hook)
-        ddp = wrap_ddp(model, device_ids=[local_rank], bucket_cap_mb=args.bucket_mb,
-                       fused_average=not args.no_fused_hook, compression="none",
-                       optimizer_in_backward=opt if in_bw else None)
-    else:
-        from torch.nn.parallel import DistributedDataParallel
-        ddp = DistributedDataParallel(model, device_ids=[local_rank], bucket_cap_mb=args.bucket_mb,
-                                      gradient_as_bucket_view=True)
-        opt = torch.optim.AdamW(ddp.parameters(), lr=1e-3, fused=True)
-    loss_fn = torch.nn.CrossEntropyLoss()
-
     local_batch = GLOBAL_BATCH // world
     assert local_batch * world == GLOBAL_BATCH, "global batch 256 must divide by the world size"
     g = torch.Generator().manual_seed(1234 + rank)
@@ -163,54 +144,117 @@ def main():
     dev_y = [t.to(dev) for t in host_y]
     h2d_bytes = host_x[0].nbytes + host_y[0].nbytes
     d2h_bytes = 4
+    loss_fn = torch.nn.CrossEntropyLoss()
+    warmup = max(args.warmup, 3)
 
-    def train_step(x, y):
-        opt.zero_grad()  # set_to_none: DDP re-points grads at its bucket views, no memset pass
-        loss = loss_fn(ddp(x), y)
-        loss.backward()
-        opt.step()
-        return loss
+    def run_arm(kind, fused_optim, group):
+        """One complete measurement (warm-up, device-timed region, end-to-end region) of one arm.
 
-    def timed(region_steps, e2e):
-        torch.cuda.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
-        sampler = ClockSampler(local_rank)
-        sampler.start()
-        launches0 = native._kernel_launches() if native else 0
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0 = time.perf_counter()
-        start.record()
-        last = None
-        for i in range(region_steps):
-            if e2e:
-                x = host_x[i % n_host_batches].to(dev, non_blocking=True)
-                y = host_y[i % n_host_batches].to(dev, non_blocking=True)
-                last = train_step(x, y).item()  # device -> host read of the step's result
-            else:
-                last = train_step(dev_x[i % n_host_batches], dev_y[i % n_host_batches])
-        end.record()
-        torch.cuda.synchronize()
-        wall_ms = (time.perf_counter() - t0) * 1e3
-        dist.barrier()
-        torch.cuda.synchronize()
-        clocks = sampler.stop()
-        launches = (native._kernel_launches() - launches0) if native else 0
-        dev_ms = start.elapsed_time(end)
-        # e2e is a host-visible quantity: take the larger of device and wall time
-        ms = max(dev_ms, wall_ms) if e2e else dev_ms
-        t = torch.tensor([ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        if not e2e and not isinstance(last, float):
-            last = float(last.item())
-        return float(t.item()), clocks, launches, last
+        kind "mccl": this backend + fused-average hook (+ fused AdamW when `fused_optim`);
+        kind "nccl": torch's NCCL backend + stock DDP + torch.optim.AdamW(fused=True).
+        `group` is the process group the arm trains on (None: the default group).
+        """
+        torch.manual_seed(42)
+        model = MLP94M().to(dev)
+        n_params = num_parameters(model)
+        in_bw = False
+        if kind == "mccl":
+            from mccl_b200.parallel import wrap_ddp
+            from mccl_b200.optim import FusedAdamW
+            opt = (FusedAdamW(model.parameters(), lr=1e-3) if fused_optim
+                   else torch.optim.AdamW(model.parameters(), lr=1e-3, fused=True))
+            in_bw = args.optim_in_backward == "on" and fused_optim and not args.no_fused_hook
+            ddp = wrap_ddp(model, device_ids=[local_rank], bucket_cap_mb=args.bucket_mb,
+                           fused_average=not args.no_fused_hook, compression="none", process_group=group,
+                           optimizer_in_backward=opt if in_bw else None)
+        else:
+            from torch.nn.parallel import DistributedDataParallel
+            ddp = DistributedDataParallel(model, device_ids=[local_rank], bucket_cap_mb=args.bucket_mb,
+                                          gradient_as_bucket_view=True, process_group=group)
+            opt = torch.optim.AdamW(ddp.parameters(), lr=1e-3, fused=True)
 
-    for i in range(max(args.warmup, 3)):
-        train_step(dev_x[i % n_host_batches], dev_y[i % n_host_batches])
-    ms_total, clocks, launches, loss_a = timed(args.steps, e2e=False)
-    for i in range(3):
-        train_step(host_x[i].to(dev, non_blocking=True), host_y[i].to(dev, non_blocking=True)).item()
-    ms_e2e, clocks_e2e, _, loss_b = timed(args.steps, e2e=True)
+        def train_step(x, y):
+            opt.zero_grad()  # set_to_none: DDP re-points grads at its bucket views, no memset pass
+            loss = loss_fn(ddp(x), y)
+            loss.backward()
+            opt.step()
+            return loss
+
+        def timed(region_steps, e2e):
+            torch.cuda.synchronize()
+            dist.barrier(group=group)
+            torch.cuda.synchronize()
+            sampler = ClockSampler(local_rank)
+            sampler.start()
+            launches0 = native._kernel_launches() if native else 0
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            start.record()
+            last = None
+            for i in range(region_steps):
+                if e2e:
+                    x = host_x[i % n_host_batches].to(dev, non_blocking=True)
+                    y = host_y[i % n_host_batches].to(dev, non_blocking=True)
+                    last = train_step(x, y).item()  # device -> host read of the step's result
+                else:
+                    last = train_step(dev_x[i % n_host_batches], dev_y[i % n_host_batches])
+            end.record()
+            torch.cuda.synchronize()
+            wall_ms = (time.perf_counter() - t0) * 1e3
+            dist.barrier(group=group)
+            torch.cuda.synchronize()
+            clocks = sampler.stop()
+            launches = (native._kernel_launches() - launches0) if native else 0
+            dev_ms = start.elapsed_time(end)
+            # e2e is a host-visible quantity: take the larger of device and wall time
+            ms = max(dev_ms, wall_ms) if e2e else dev_ms
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+            if not e2e and not isinstance(last, float):
+                last = float(last.item())
+            return float(t.item()), clocks, launches, last
+
+        for i in range(warmup):
+            train_step(dev_x[i % n_host_batches], dev_y[i % n_host_batches])
+        ms_total, clocks, launches, _ = timed(args.steps, e2e=False)
+        for i in range(3):
+            train_step(host_x[i].to(dev, non_blocking=True), host_y[i].to(dev, non_blocking=True)).item()
+        ms_e2e, clocks_e2e, _, loss_b = timed(args.steps, e2e=True)
+        del ddp, opt, model
+        torch.cuda.empty_cache()
+        return {"ms_total": ms_total, "ms_e2e": ms_e2e, "clocks": clocks, "clocks_e2e": clocks_e2e,
+                "launches": launches, "final_loss": loss_b, "n_params": n_params, "in_bw": in_bw,
+                "value": GLOBAL_BATCH / (ms_total / args.steps / 1e3),
+                "e2e_value": GLOBAL_BATCH / (ms_e2e / args.steps / 1e3)}
+
+    main_arm = run_arm(args.impl, not args.no_fused_optim, None)
+    ms_total, ms_e2e = main_arm["ms_total"], main_arm["ms_e2e"]
+    clocks, clocks_e2e, launches, loss_b = main_arm["clocks"], main_arm["clocks_e2e"], main_arm["launches"], main_arm["final_loss"]
+    n_params, in_bw = main_arm["n_params"], main_arm["in_bw"]
+
+    # Comparison arms in the same process, on the same GPUs, with the same steps and warm-up:
+    # (a) this backend with torch's own fused AdamW, which isolates the communication path from the
+    # optimizer kernel, and (b) torch's stock NCCL backend + stock DDP + torch AdamW.
+    extra = {}
+    if args.impl == "mccl" and not args.no_compare:
+        if not args.no_fused_optim:
+            arm = run_arm("mccl", False, None)
+            extra["no_fused_optim"] = {"value": round(arm["value"], 2), "e2e": round(arm["e2e_value"], 2),
+                                       "ms_per_step": round(arm["ms_total"] / args.steps, 4), "clocks": arm["clocks"]}
+        try:
+            nccl_group = dist.new_group(backend="nccl")
+            arm = run_arm("nccl", False, nccl_group)
+            extra["nccl_value"] = round(arm["value"], 2)
+            extra["nccl_e2e"] = round(arm["e2e_value"], 2)
+            extra["nccl_ms_per_step"] = round(arm["ms_total"] / args.steps, 4)
+            extra["nccl_clocks"] = arm["clocks"]
+            extra["vs_nccl"] = round(main_arm["value"] / arm["value"], 4)
+            extra["vs_nccl_e2e"] = round(main_arm["e2e_value"] / arm["e2e_value"], 4)
+            if "no_fused_optim" in extra:
+                extra["no_fused_optim"]["vs_nccl"] = round(extra["no_fused_optim"]["value"] / arm["value"], 4)
+                extra["no_fused_optim"]["vs_nccl_e2e"] = round(extra["no_fused_optim"]["e2e"] / arm["e2e_value"], 4)
+        except Exception as exc:  # the comparison must never take the headline down with it
+            extra["nccl_error"] = f"{type(exc).__name__}: {exc}"[:300]
 
     ms_per_step = ms_total / args.steps
     value = GLOBAL_BATCH / (ms_per_step / 1e3)
@@ -226,7 +270,7 @@ def main():
         "unit": "samples/s",
         "n_gpus": world,
         "steps": args.steps,
-        "warmup": max(args.warmup, 3),
+        "warmup": warmup,
         "ms_per_step": round(ms_per_step, 4),
         "higher_is_better": True,
         "scaling": "strong",
@@ -253,6 +297,7 @@ def main():
         "gpu_launches": launches,
         "final_loss": loss_b,
     }
+    out.update(extra)
     if rank == 0:
         print(json.dumps(out), flush=True)
     dist.destroy_process_group()

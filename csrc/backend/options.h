@@ -57,7 +57,14 @@ struct MCCLOptions : c10d::Backend::Options {
   std::chrono::milliseconds heartbeat_interval{5000};
 
   // B200 data plane
-  std::string algo = "auto";            // auto | oneshot | twoshot | staged
+  std::string algo = "auto";            // auto | oneshot | twoshot | nvls | staged
+  std::string nvls = "auto";            // auto | 0 | 1 : NVLS (multimem) region and kernels; auto = use when the
+                                        // devices support NVLink multicast, 0 = never create it, 1 = warn if unavailable
+  int64_t nvls_bytes = 64ll << 20;      // one NVLS buffer (4 per rank)
+  int64_t nvls_min_bytes = -2;          // allreduce: smallest payload for the NVLS kernel (-2: tuner table, -1: never)
+  int64_t nvls_split_min_bytes = -2;    // NVLS allreduce: staging as separate kernels from this size (-2: tuner, -1: never)
+  int64_t tile_bytes = 0;               // pipeline tile of the byte movers / NVLS kernels (0: tuner table)
+  bool debug_checks = false;            // kernels verify their buffer ranges and report ERR_BOUNDS
   int64_t oneshot_max_bytes = -1;       // -1: tuner table
   int64_t comm_ctas = 0;                // 0: from message size
   int64_t tiles = 1;                    // two-shot pipeline tiles per CTA (1: bulk phases)
@@ -88,6 +95,12 @@ struct MCCLOptions : c10d::Backend::Options {
     o->algo = env_str("MCCL_ALGO", "auto");
     o->oneshot_max_bytes = env_int("MCCL_ONESHOT_MAX_BYTES", -1);
     o->comm_ctas = env_int("MCCL_COMM_CTAS", 0);
+    o->nvls = env_str("MCCL_NVLS", "auto");
+    o->nvls_bytes = env_int("MCCL_NVLS_BYTES", 64ll << 20);
+    o->nvls_min_bytes = env_int("MCCL_NVLS_MIN_BYTES", -2);
+    o->nvls_split_min_bytes = env_int("MCCL_NVLS_SPLIT_MIN_BYTES", -2);
+    o->tile_bytes = env_int("MCCL_TILE_BYTES", 0);
+    o->debug_checks = env_bool("MCCL_DEBUG_CHECKS", false);
     o->tiles = env_int("MCCL_TILES", 1);
     o->gather = env_str("MCCL_GATHER", "auto");
     // MCCL_COLLECTIVE_CONCURRENCY, when set, caps the lanes (1 = strictly one collective at a time)

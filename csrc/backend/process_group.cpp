@@ -59,8 +59,9 @@ ProcessGroupMCCL::ProcessGroupMCCL(const c10::intrusive_ptr<c10d::Store>& store,
     MCCL_WARN("MCCL_GATHER=%s is not one of auto|pull|push: using auto", options_->gather.c_str());
     options_->gather = "auto";
   }
-  if (options_->algo != "auto" && options_->algo != "oneshot" && options_->algo != "twoshot" && options_->algo != "staged") {
-    MCCL_WARN("MCCL_ALGO=%s is not one of auto|oneshot|twoshot|staged: using auto", options_->algo.c_str());
+  if (options_->algo != "auto" && options_->algo != "oneshot" && options_->algo != "twoshot" && options_->algo != "nvls" &&
+      options_->algo != "staged") {
+    MCCL_WARN("MCCL_ALGO=%s is not one of auto|oneshot|twoshot|nvls|staged: using auto", options_->algo.c_str());
     options_->algo = "auto";
   }
   device_timing_ = static_cast<int>(std::max<int64_t>(0, env_int("MCCL_DEVICE_TIMING", 8)));
@@ -75,6 +76,13 @@ ProcessGroupMCCL::ProcessGroupMCCL(const c10::intrusive_ptr<c10d::Store>& store,
   if (options_->oneshot_max_bytes >= 0)
     for (int ws = 0; ws <= kern::kMaxWorld; ++ws)
       tuner_.set_oneshot_max_bytes(ws, static_cast<size_t>(options_->oneshot_max_bytes));
+  if (options_->nvls_min_bytes >= -1)
+    for (int ws = 0; ws <= kern::kMaxWorld; ++ws) tuner_.set_nvls_min_bytes(ws, options_->nvls_min_bytes);
+  if (options_->comm_ctas > kern::kMaxCtasPerLane) {
+    MCCL_WARN("MCCL_COMM_CTAS=%lld exceeds the %d CTAs one lane may use (two lanes must stay co-resident): clamped",
+              (long long)options_->comm_ctas, kern::kMaxCtasPerLane);
+    options_->comm_ctas = kern::kMaxCtasPerLane;
+  }
 
   MCCL_TRACE("ctor: tuner ok");
   rendezvous_ = std::make_unique<Rendezvous>(store_, rank, size);
@@ -126,7 +134,8 @@ std::string ProcessGroupMCCL::describe() const {
     << " overlap_comm=" << options_->overlap_comm << " arena=" << (options_->arena_bytes >> 20) << "MiB x4"
     << " oneshot_max(ws)=" << tuner_.oneshot_max_bytes(std::min(getSize(), kern::kMaxWorld))
     << " segment=" << (tuner_.segment_bytes() >> 20) << "MiB"
-    << " lanes=" << options_->lanes << " comm_ctas=" << options_->comm_ctas << " wire_dtype=" << options_->wire_dtype
+    << " lanes=" << options_->lanes << " comm_ctas=" << options_->comm_ctas << " nvls=" << options_->nvls
+    << " wire_dtype=" << options_->wire_dtype
     << " compression=" << (compressor_ ? compressor_->name() : std::string("none"))
     << " topk_ratio=" << options_->topk_ratio << " watchdog_ms=" << options_->watchdog_timeout.count()
     << " heartbeat_ms=" << options_->heartbeat_interval.count()
@@ -156,6 +165,8 @@ void ProcessGroupMCCL::shutdown() {
     if (nccl_p2p_) nccl_p2p_->shutdown();
     nccl_p2p_.reset();
   }
+  release_nvls();
+  arena_quick_.store(nullptr, std::memory_order_release);
   cuda_.reset();
 }
 
@@ -485,8 +496,10 @@ void ProcessGroupMCCL::cpu_allreduce(uint32_t seq, at::Tensor& t, c10d::ReduceOp
     }
     PhaseTimer pt{metrics_, seq, Metrics::Phase::REDUCE};
     // Fixed rank order: acc = x0 op x1 op ... ; `data` holds x_me.  With two ranks the
-    // operation is a single commutative elementwise op (IEEE add/mul/min/max give the same
-    // bits for either operand order), so both ranks reduce in place without the reordering copies.
+    // operation is a single elementwise op that gives the same bits for either operand order
+    // (IEEE add and mul are commutative; MIN / MAX are made so in cpu/reduce.cpp: NaNs propagate
+    // as the canonical NaN and -0 orders below +0), so both ranks reduce in place without the
+    // reordering copies.
     if (ws == 2) {
       cpu_reduce_into(data, bufs[1 - me].data(), n, dtype, op);
     } else if (me != 0) {

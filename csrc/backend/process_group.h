@@ -103,9 +103,11 @@ class ProcessGroupMCCL : public c10d::Backend {
   void log_metrics();
   void reset_metrics();
   bool poisoned() const { return poisoned_.load(); }
+  // A kernel's bounded wait has given up (read from host-mapped memory: no stream involved).
+  bool device_failed_quick() const;
   std::string poison_reason() const;
   std::string describe() const;   // one-line configuration dump
-  std::string data_plane() const; // "nvlink-p2p", "host-staged", "local", "uninitialised"
+  std::string data_plane() const; // "nvlink-p2p", "nvlink-p2p+nvls", "host-staged", "local", "uninitialised"
   // Fused compressed allreduce (top-k + error feedback) on a CUDA bucket.
   c10::intrusive_ptr<c10d::Work> allreduce_topk(at::Tensor& grad, at::Tensor& residual, double ratio,
                                                 float scale);
@@ -160,6 +162,7 @@ class ProcessGroupMCCL : public c10d::Backend {
   c10::intrusive_ptr<c10d::Work> staged_via_host(c10d::OpType op, std::vector<at::Tensor> cuda_tensors,
                                                  std::function<c10::intrusive_ptr<c10d::Work>(std::vector<at::Tensor>&)> fn,
                                                  bool copy_back);
+  void release_nvls();  // ordered tear-down of the NVLS region (drain streams, meet the peers, unbind)
   void poll_device(bool must = false);  // watchdog hook: status block + event-timed metrics
   void drain_finished();
   void device_health_check();
@@ -201,6 +204,7 @@ class ProcessGroupMCCL : public c10d::Backend {
   // CUDA state
   struct CudaState;
   std::shared_ptr<CudaState> cuda_;  // shared_ptr: destructible where the type is incomplete
+  std::atomic<const SymmetricArena*> arena_quick_{nullptr};  // cuda_->arena for lock-free status reads
   std::mutex cuda_mu_;
 };
 

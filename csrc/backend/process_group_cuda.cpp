@@ -13,11 +13,13 @@
 #include <c10/cuda/CUDACachingAllocator.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <cuda_runtime_api.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include "backend/process_group.h"
 #include "backend/tensor_checks.h"
 #include "common/log.h"
 #include "kernels/topk_api.h"
+#include "runtime/nvls.h"
 
 namespace mccl {
 
@@ -32,12 +34,21 @@ struct ProcessGroupMCCL::CudaState {
   cudaEvent_t join_ev = nullptr;
   cudaStream_t poll_stream = nullptr;
   std::unique_ptr<SymmetricArena> arena;
+  std::unique_ptr<NvlsRegion> nvls;  // multicast-bound buffers (nullptr: not supported / switched off)
   bool p2p = false;
+  bool stamps_always = false;  // MCCL_PHASE_STAMPS=1: every collective stamps, not only the timed ones
   std::string why_not;
   at::cuda::CUDAEvent fence{cudaEventDisableTiming};
   struct Pending {
     uint32_t seq;
     cudaEvent_t start, end;
+    const char* name;     // collective, for the INFO line
+    const char* algo;     // kernel variant
+    uint64_t bytes;       // payload of this rank
+    double bus_factor;    // busbw = bytes / t * bus_factor
+    double sync_ms;       // host time spent fencing streams for this collective
+    bool stamps;          // phase stamps were captured for it
+    int64_t stamp_epoch;  // arena epoch of its last launch
   };
   std::deque<Pending> pending;
   std::vector<cudaEvent_t> free_events;
@@ -64,6 +75,7 @@ struct ProcessGroupMCCL::CudaState {
     for (auto e : lane_done)
       if (e) cudaEventDestroy(e);
     if (join_ev) cudaEventDestroy(join_ev);
+    nvls.reset();
     arena.reset();
     if (poll_stream) cudaStreamDestroy(poll_stream);
   }
@@ -72,7 +84,32 @@ struct ProcessGroupMCCL::CudaState {
 std::string ProcessGroupMCCL::data_plane() const {
   if (getSize() == 1) return "local";
   if (!cuda_) return "uninitialised";
-  return cuda_->p2p ? "nvlink-p2p" : "host-staged";
+  return cuda_->p2p ? (cuda_->nvls ? "nvlink-p2p+nvls" : "nvlink-p2p") : "host-staged";
+}
+
+bool ProcessGroupMCCL::device_failed_quick() const {
+  const SymmetricArena* a = arena_quick_.load(std::memory_order_acquire);
+  return a != nullptr && a->device_failed();
+}
+
+// Ordered tear-down of the NVLS region.  Memory bound to a multicast object must not disappear
+// while a peer can still issue a multimem access to it, so: drain this rank's communication
+// streams, meet the peers at a host-side rendezvous (bounded: a peer that is gone cannot be waited
+// for), and only then unmap and unbind.
+void ProcessGroupMCCL::release_nvls() {
+  std::lock_guard<std::mutex> g(cuda_mu_);
+  if (!cuda_ || !cuda_->nvls) return;
+  c10::cuda::OptionalCUDAGuard guard(cuda_->dev);
+  for (auto& l : cuda_->lanes) cudaStreamSynchronize(l.stream());
+  cudaDeviceSynchronize();
+  cudaGetLastError();
+  try {
+    rendezvous_->exchange("nvls_bye", "bye", std::chrono::milliseconds(env_int("MCCL_NVLS_BYE_TIMEOUT_MS", 5000)));
+  } catch (const std::exception& e) {
+    MCCL_WARN("rank %d: peers did not all reach the NVLS tear-down rendezvous (%s); releasing anyway", getRank(), e.what());
+  }
+  cuda_->nvls->release();
+  cuda_->nvls.reset();
 }
 
 void ProcessGroupMCCL::ensure_cuda(c10::DeviceIndex dev) {
@@ -139,7 +176,26 @@ void ProcessGroupMCCL::ensure_cuda(c10::DeviceIndex dev) {
     MCCL_INFO("rank %d: NVLink peer arena mapped on %d ranks (%lld MiB x2 per rank)", getRank(), ws,
               (long long)(options_->arena_bytes >> 20));
   }
-  if (st->arena && env_bool("MCCL_PHASE_STAMPS", false)) st->arena->enable_stamps(true);
+  // Phase stamps (seven %globaltimer reads by one thread per kernel) feed the reduce/network split of
+  // the metrics for the timed collectives; MCCL_PHASE_STAMPS=0 switches them off.
+  if (st->arena && (device_timing_ > 0 || env_bool("MCCL_PHASE_STAMPS", false)) && env_bool("MCCL_PHASE_STAMPS", true))
+    st->arena->enable_stamps(true);
+  st->stamps_always = std::getenv("MCCL_PHASE_STAMPS") != nullptr && env_bool("MCCL_PHASE_STAMPS", false);
+  // NVLS region: collective set-up with agreement rounds, so either every rank has it or none.
+  if (st->p2p && ws >= 2 && options_->nvls != "0" && options_->nvls != "off") {
+    std::string why;
+    st->nvls = NvlsRegion::create(
+        getRank(), ws, static_cast<size_t>(options_->nvls_bytes), kern::kNumParity, "pg",
+        [this, timeout](const std::string& tag, const std::string& mine) { return rendezvous_->exchange(tag, mine, timeout); },
+        &why);
+    if (!st->nvls) {
+      if (options_->nvls == "1" || options_->nvls == "on" || options_->algo == "nvls")
+        MCCL_WARN("rank %d: NVLS requested but unavailable (%s); using the peer-memory kernels", getRank(), why.c_str());
+      else
+        MCCL_INFO("rank %d: NVLS not used (%s)", getRank(), why.c_str());
+    }
+  }
+  arena_quick_.store(st->arena.get(), std::memory_order_release);
   cuda_ = std::move(st);
 }
 
@@ -173,8 +229,27 @@ void ProcessGroupMCCL::drain_finished() {
       cudaGetLastError();
       ms = 0.f;
     }
-    metrics_.record_phase(p.seq, Metrics::Phase::NETWORK, ms);
+    // Phase split: SYNC = host time spent ordering streams, REDUCE = device time of the reduction
+    // phase when the in-kernel stamps are on (stamp 3 -> 4), NETWORK = the rest of the device time.
+    double reduce_ms = 0.0;
+    if (p.stamps && cs.arena) {
+      unsigned long long st[kern::kStampSlots];
+      try {
+        cs.arena->read_stamps(st, cs.poll_stream, 0, p.stamp_epoch);
+        // share of the kernel spent between "peers' data seen" and "reduction done"; for a
+        // segmented collective the last segment's share stands for all of them
+        if (st[0] != 0 && st[3] >= st[0] && st[4] > st[3] && st[6] >= st[4] && st[6] > st[0])
+          reduce_ms = ms * static_cast<double>(st[4] - st[3]) / static_cast<double>(st[6] - st[0]);
+      } catch (const std::exception&) {
+      }
+    }
+    metrics_.record_phase(p.seq, Metrics::Phase::SYNC, p.sync_ms);
+    metrics_.record_phase(p.seq, Metrics::Phase::REDUCE, reduce_ms);
+    metrics_.record_phase(p.seq, Metrics::Phase::NETWORK, ms - reduce_ms);
     metrics_.op_end_timed(p.seq, ms);
+    if (log_enabled(LogLevel::INFO) && p.name != nullptr)
+      MCCL_INFO("%s seq=%u algo=%s bytes=%llu device_us=%.1f busbw=%.2f GB/s", p.name, p.seq, p.algo ? p.algo : "-",
+                (unsigned long long)p.bytes, ms * 1e3, ms > 0.f ? static_cast<double>(p.bytes) * p.bus_factor / (ms * 1e6) : 0.0);
     watchdog_->complete(p.seq);
     cs.free_events.push_back(p.start);
     cs.free_events.push_back(p.end);
@@ -270,19 +345,36 @@ struct CudaPath {
   cudaEvent_t ev_start = nullptr, ev_end = nullptr;
   bool skip = false;
   std::function<void(cudaStream_t)> epilogue;  // enqueued behind the collective, covered by the Work
+  const char* op_name;
+  const char* algo = nullptr;    // kernel variant of the last launch (INFO line)
+  uint64_t payload;
+  double bus_factor = 1.0;       // busbw = payload / t * bus_factor
+  double sync_ms = 0.0;          // host time spent in producer fences
+  bool reducing = false;         // the kernels of this collective write reduction-phase stamps
+  int64_t last_epoch = -1;
+  bool range_open = false;
 
   CudaPath(ProcessGroupMCCL& pg_, c10d::OpType op, const char* name, uint64_t bytes, std::vector<at::Tensor> outs,
            c10::DeviceIndex dev, bool serial_ = false)
       : pg(pg_), cs(*pg_.cuda_), seq(pg_.next_seq()), caller(c10::cuda::getCurrentCUDAStream(dev)),
         stream(caller), serial(serial_ || pg_.options_->lanes < 2), overlap(pg_.options_->overlap_comm),
-        timing(pg_.device_timing_ > 0 && (pg_.timing_tick_++ % static_cast<uint32_t>(pg_.device_timing_)) == 0) {
+        timing(pg_.device_timing_ > 0 && (pg_.timing_tick_++ % static_cast<uint32_t>(pg_.device_timing_)) == 0),
+        op_name(name), payload(bytes) {
+    // a bounded device-side wait that gave up earlier poisons the group before anything new is enqueued
+    if (pg.device_failed_quick()) pg.poll_device(/*must=*/true);
     pg.check_alive(name);
+    nvtxRangePushA(name);  // one range per collective around its launches (visible to attached profilers)
+    range_open = true;
     work = c10::make_intrusive<WorkMCCL>(pg.getRank(), op, seq, pg.profile_titles_ ? name : nullptr, std::move(outs),
                                          /*stream_mode=*/true, dev);
     pg.metrics_.op_start(seq, name, bytes);
     pg.watchdog_->watch(seq, name);
     if (overlap && serial) use_stream(cs.lanes[0]);  // temporaries of serial collectives live on lane stream 0
     skip = pg.skip_next_launch_.exchange(false);
+  }
+
+  ~CudaPath() {
+    if (range_open) nvtxRangePop();
   }
 
   // First use of `s` by this collective: order it behind the producer and tell the allocator.
@@ -292,12 +384,14 @@ struct CudaPath {
       if (used[i] == s.stream()) return;
     used[n_used++] = s.stream();
     if (s != caller) {
+      const auto t0 = timing ? std::chrono::steady_clock::now() : std::chrono::steady_clock::time_point();
       if (!fenced) {
         cs.fence.record(caller);
         fenced = true;
       }
       cs.fence.block(s);
       for (auto& t : kept) c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), s);
+      if (timing) sync_ms += ms_since(t0);
     }
     if (n_used == 1) {
       pg.metrics_.op_execute_start(seq);
@@ -335,9 +429,19 @@ struct CudaPath {
       MCCL_CUDA_CHECK(cudaStreamWaitEvent(stream.stream(), cs.lane_done[lane], 0));
     }
     cur_lane = lane;
+    last_epoch = epoch;
     p.scale = 1.0f;
     p.wait_ns = static_cast<unsigned long long>(pg.options_->device_wait_us) * 1000ull;
     p.tiles = static_cast<int>(pg.options_->tiles);
+    p.tile_bytes = static_cast<int>(pg.options_->tile_bytes);
+    p.debug_checks = pg.options_->debug_checks ? 1 : 0;
+    if (!timing && !cs.stamps_always) p.ctx[0].stamps = nullptr;  // stamps are read back for timed collectives only
+    if (cs.nvls) {
+      p.ctx[0].nvls_uc = cs.nvls->uc();
+      p.ctx[0].nvls_mc = cs.nvls->mc();
+      p.nvls_offset = cs.nvls->buffer_offset(epoch);
+      p.nvls_capacity = cs.nvls->buffer_bytes();
+    }
     return p;
   }
 
@@ -385,7 +489,8 @@ struct CudaPath {
       bool crowded;
       {
         std::lock_guard<std::mutex> g(cs.pending_mu);
-        cs.pending.push_back({seq, ev_start, ev_end});
+        cs.pending.push_back({seq, ev_start, ev_end, op_name, algo, payload, bus_factor, sync_ms,
+                              reducing && cs.arena && cs.arena->stamps_enabled(), last_epoch});
         crowded = cs.pending.size() > 64;
       }
       if (crowded) pg.drain_finished();  // keep the event pool small between watchdog polls
@@ -395,6 +500,11 @@ struct CudaPath {
     }
     ProcessGroupMCCL* self = &pg;
     work->set_health_check([self] { self->device_health_check(); });
+    work->set_quick_check([self] { return self->device_failed_quick(); });
+    if (range_open) {
+      nvtxRangePop();
+      range_open = false;
+    }
     work->attach_stream(stream, blocking || pg.options_->blocking_wait);
     return work;
   }
@@ -446,21 +556,32 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allreduce(at::Tensor& t, c
   CudaPath cp(*this, c10d::OpType::ALLREDUCE, "mccl:all_reduce", t.nbytes(), {t}, dev);
   cp.epilogue = std::move(epilogue);
   cp.keep(t);
+  cp.reducing = true;
+  cp.bus_factor = 2.0 * (ws - 1) / ws;
 
-  // Segment so that every launch fits one parity buffer.
+  const int cls = wsz <= 2 ? 1 : 0;
+  const bool nvls_ok = cuda_->nvls != nullptr && kern::nvls_allreduce_supported(dt, wire, to_kern_op(op)) &&
+                       options_->algo != "oneshot" && options_->algo != "twoshot";
+  // Segment so that every launch fits one parity buffer (and one NVLS buffer when that path is taken).
   const size_t cap = cuda_->arena->parity_bytes();
-  int64_t seg_elems = static_cast<int64_t>(std::min(tuner_.segment_bytes(), cap * ws / (ws + 1)) / wsz);
+  size_t seg_bytes = std::min(tuner_.segment_bytes(), cap * ws / (ws + 1));
+  const bool whole_nvls = nvls_ok && (options_->algo == "nvls" ||
+                                      tuner_.choose_allreduce(ws, static_cast<size_t>(n) * wsz, cls, true) == Variant::NVLS);
+  if (whole_nvls) seg_bytes = std::min(seg_bytes, cuda_->nvls->buffer_bytes() / 4096 * 4096);
+  int64_t seg_elems = static_cast<int64_t>(seg_bytes / wsz);
   seg_elems = std::max<int64_t>(seg_elems / 256 * 256, 256);
   char* base = static_cast<char*>(t.data_ptr());
   uint64_t sent = 0;
   for (int64_t off = 0; off < n; off += seg_elems) {
     const int64_t cnt = std::min(seg_elems, n - off);
     const size_t wire_bytes = static_cast<size_t>(cnt) * wsz;
-    Variant v = tuner_.choose_allreduce(ws, wire_bytes);
+    Variant v = tuner_.choose_allreduce(ws, wire_bytes, cls, nvls_ok);
     if (options_->algo == "oneshot") v = Variant::ONESHOT;
     if (options_->algo == "twoshot") v = Variant::TWOSHOT;
+    if (options_->algo == "nvls" && nvls_ok) v = Variant::NVLS;
+    if (v == Variant::NVLS && kern::nvls_allreduce_stage_bytes(wire_bytes, ws) > cuda_->nvls->buffer_bytes()) v = Variant::TWOSHOT;
     if (v == Variant::ONESHOT && kern::oneshot_arena_bytes(wire_bytes, ws) > cap) v = Variant::TWOSHOT;
-    MCCL_CHECK(kern::twoshot_arena_bytes(wire_bytes, ws) <= cap, "segment does not fit the arena");
+    MCCL_CHECK(v == Variant::NVLS || kern::twoshot_arena_bytes(wire_bytes, ws) <= cap, "segment does not fit the arena");
     bool push = options_->gather == "push" || (options_->gather == "auto" && tuner_.push_gather(ws));
     if (push && kern::twoshot_arena_bytes(wire_bytes, ws, true) > cap) push = false;
     kern::CollParams p = cp.params();
@@ -470,15 +591,22 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allreduce(at::Tensor& t, c
     p.count = cnt;
     p.op = to_kern_op(op);
     p.scale = (op == c10d::ReduceOp::AVG ? 1.0f / ws : 1.0f) * prescale;
+    if (v == Variant::NVLS && p.tile_bytes == 0) p.tile_bytes = tuner_.nvls_tile_bytes();
+    const int64_t split_min = options_->nvls_split_min_bytes >= -1 ? options_->nvls_split_min_bytes : tuner_.nvls_split_min_bytes();
+    const bool nvls_split = v == Variant::NVLS && split_min >= 0 && static_cast<int64_t>(wire_bytes) >= split_min;
     if (!cp.skip) {
       if (v == Variant::ONESHOT)
         MCCL_LAUNCH_CHECK(kern::launch_allreduce_oneshot(p, dt, wire, cp.cfg(wire_bytes * (ws - 1), overlapped), cp.stream.stream()));
+      else if (v == Variant::NVLS)
+        MCCL_LAUNCH_CHECK(kern::launch_allreduce_nvls(p, dt, wire, cp.cfg(wire_bytes, overlapped), cp.stream.stream(), nvls_split));
       else
         MCCL_LAUNCH_CHECK(kern::launch_allreduce_twoshot(p, dt, wire, cp.cfg(wire_bytes, overlapped), cp.stream.stream()));
     }
-    sent += v == Variant::ONESHOT ? wire_bytes * (ws - 1) : 2 * wire_bytes * (ws - 1) / ws;
-    MCCL_DEBUG("allreduce seq=%u epoch=%u %s bytes=%zu wire=%d", cp.seq, p.seq,
-               v == Variant::ONESHOT ? "oneshot" : "twoshot", wire_bytes, int(wire));
+    cp.algo = nvls_split ? "nvls-split" : variant_name(v);
+    sent += v == Variant::ONESHOT ? wire_bytes * (ws - 1)
+            : v == Variant::NVLS  ? wire_bytes + wire_bytes / ws
+                                  : 2 * wire_bytes * (ws - 1) / ws;
+    MCCL_DEBUG("allreduce seq=%u epoch=%u %s bytes=%zu wire=%d", cp.seq, p.seq, variant_name(v), wire_bytes, int(wire));
   }
   metrics_.record_transport_bytes(sent, sent);
   return cp.finish();
@@ -500,8 +628,11 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_broadcast(at::Tensor& t, i
   c10::cuda::CUDAGuard guard(dev);
   CudaPath cp(*this, c10d::OpType::BROADCAST, "mccl:broadcast", t.nbytes(), {t}, dev);
   cp.keep(t);
-  const size_t cap = cuda_->arena->parity_bytes() / 256 * 256;
+  const int ws = getSize();
   const size_t nbytes = t.nbytes();
+  const bool nvls = cuda_->nvls != nullptr && options_->algo != "oneshot" && options_->algo != "twoshot" &&
+                    (options_->algo == "nvls" || tuner_.broadcast_nvls(ws, nbytes));
+  const size_t cap = (nvls ? std::min(cuda_->arena->parity_bytes(), cuda_->nvls->buffer_bytes()) : cuda_->arena->parity_bytes()) / 256 * 256;
   char* base = static_cast<char*>(t.data_ptr());
   for (size_t off = 0; off < nbytes; off += cap) {
     const size_t cnt = std::min(cap, nbytes - off);
@@ -510,10 +641,13 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_broadcast(at::Tensor& t, i
     p.ctx[0].out = base + off;
     p.count = static_cast<int64_t>(cnt);
     p.root = root;
+    p.use_nvls = nvls ? 1 : 0;
+    if (p.tile_bytes == 0) p.tile_bytes = tuner_.mover_tile_bytes();
     if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_broadcast(p, cp.cfg(cnt), cp.stream.stream()));
   }
+  cp.algo = nvls ? "nvls" : (ws == 2 || nbytes <= (256u << 10)) ? "direct" : "twohop";
   if (getRank() == root) metrics_.record_transport_bytes(nbytes, 0);
-  else metrics_.record_transport_bytes(nbytes / getSize(), nbytes);
+  else metrics_.record_transport_bytes(nvls ? 0 : nbytes * (ws - 2) / (ws - 1), nbytes);
   return cp.finish();
 }
 
@@ -537,7 +671,9 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allgather(at::Tensor& out_
   }
   c10::cuda::CUDAGuard guard(dev);
   std::vector<at::Tensor> outs = scatter_to ? *scatter_to : std::vector<at::Tensor>{out_flat};
-  CudaPath cp(*this, c10d::OpType::ALLGATHER, "mccl:all_gather", in.nbytes() * ws, outs, dev, /*serial=*/true);
+  // with a temporary that is scattered afterwards everything stays on one stream; otherwise the
+  // slices of a large gather alternate lanes like the segments of a large allreduce
+  CudaPath cp(*this, c10d::OpType::ALLGATHER, "mccl:all_gather", in.nbytes() * ws, outs, dev, /*serial=*/scatter_to != nullptr);
   at::Tensor flat = out_flat;
   if (scatter_to) {
     c10::cuda::CUDAStreamGuard sg(cp.stream);  // temporary belongs to the stream that uses it
@@ -545,34 +681,29 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allgather(at::Tensor& out_
   }
   cp.keep(in);
   cp.keep(flat);
-  const size_t cap = cuda_->arena->parity_bytes() / 256 * 256;
+  cp.bus_factor = static_cast<double>(ws - 1) / ws;
   const size_t nbytes = in.nbytes();
+  const bool nvls = cuda_->nvls != nullptr && options_->algo != "oneshot" && options_->algo != "twoshot" &&
+                    (options_->algo == "nvls" || tuner_.allgather_nvls(ws, nbytes));
+  // one launch stages ws blocks in every rank's staging buffer: larger blocks go slice by slice, each
+  // slice landing at its final place (the kernel takes the distance between ranks' blocks in `out`)
+  const size_t stage = nvls ? std::min(cuda_->arena->parity_bytes(), cuda_->nvls->buffer_bytes()) : cuda_->arena->parity_bytes();
+  const size_t cap = std::max<size_t>((stage / ws) / 256 * 256, 256);
   const char* ibase = static_cast<const char*>(in.data_ptr());
   char* obase = static_cast<char*>(flat.data_ptr());
-  if (nbytes <= cap) {
+  for (size_t off = 0; off < nbytes; off += cap) {
+    const size_t cnt = std::min(cap, nbytes - off);
     kern::CollParams p = cp.params();
-    p.ctx[0].in = ibase;
-    p.ctx[0].out = obase;
-    p.count = static_cast<int64_t>(nbytes);
-    if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_allgather(p, cp.cfg(nbytes * ws), cp.stream.stream()));
-  } else {
-    // Per-rank blocks larger than the arena: gather slice by slice.  The kernel
-    // places rank r's block at out + r * count, so each slice gathers into a
-    // temporary that is then scattered to its strided destination.
-    c10::cuda::CUDAStreamGuard sg(cp.stream);
-    at::Tensor tmp = at::empty({static_cast<int64_t>(ws * cap)}, in.options().dtype(at::kByte));
-    for (size_t off = 0; off < nbytes; off += cap) {
-      const size_t cnt = std::min(cap, nbytes - off);
-      kern::CollParams p = cp.params();
-      p.ctx[0].in = ibase + off;
-      p.ctx[0].out = tmp.data_ptr();
-      p.count = static_cast<int64_t>(cnt);
-      if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_allgather(p, cp.cfg(cnt * ws), cp.stream.stream()));
-      for (int r = 0; r < ws; ++r)
-        MCCL_CUDA_CHECK(cudaMemcpyAsync(obase + r * nbytes + off, static_cast<char*>(tmp.data_ptr()) + r * cnt, cnt,
-                                        cudaMemcpyDeviceToDevice, cp.stream.stream()));
-    }
+    p.ctx[0].in = ibase + off;
+    p.ctx[0].out = obase + off;
+    p.count = static_cast<int64_t>(cnt);
+    p.out_pitch = static_cast<int64_t>(nbytes);
+    p.use_nvls = nvls ? 1 : 0;
+    if (p.tile_bytes == 0) p.tile_bytes = tuner_.mover_tile_bytes();
+    MCCL_CHECK(kern::allgather_stage_bytes(cnt, ws) <= stage, "allgather slice does not fit the staging buffer");
+    if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_allgather(p, cp.cfg(cnt * ws), cp.stream.stream()));
   }
+  cp.algo = nvls ? "nvls-push" : "push";
   if (scatter_to) {
     c10::cuda::CUDAStreamGuard sg(cp.stream);
     for (int r = 0; r < ws; ++r) {

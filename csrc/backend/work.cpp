@@ -102,6 +102,11 @@ bool WorkMCCL::wait(std::chrono::milliseconds timeout) {
       std::lock_guard<std::mutex> lk(mutex_);
       if (exception_) std::rethrow_exception(exception_);
     }
+    // A bounded device-side wait that already gave up is visible in host memory: fail now instead
+    // of letting the caller consume a result that was never produced.  (A failure that happens
+    // after this point is caught by the next wait, the next launch, or the watchdog poll; results
+    // between the failure and its detection are undefined.)
+    if (quick_check_ && quick_check_() && health_check_) health_check_();
     synchronize();
     const bool blocking = blocking_wait_ || timeout != kNoTimeout;
     if (blocking && done_) {

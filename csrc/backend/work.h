@@ -56,6 +56,9 @@ class WorkMCCL : public c10d::Work {
   }
   // Runs after the device work is known complete in a blocking wait; may throw.
   void set_health_check(std::function<void()> fn) { health_check_ = std::move(fn); }
+  // Cheap test run by every wait(), blocking or not: returns true when the device has already
+  // reported a failure (the full health check then runs and throws).
+  void set_quick_check(std::function<bool()> fn) { quick_check_ = std::move(fn); }
 
   uint32_t seq() const { return seq_; }
   bool stream_mode() const { return stream_mode_; }
@@ -73,6 +76,7 @@ class WorkMCCL : public c10d::Work {
   std::unique_ptr<c10::cuda::CUDAStream> comm_;  // stream the collective was enqueued on
   c10::intrusive_ptr<c10::ivalue::Future> future_;
   std::function<void()> health_check_;
+  std::function<bool()> quick_check_;
 };
 
 }  // namespace mccl

@@ -31,6 +31,8 @@
 #include "kernels/launch_count.h"
 #include "kernels/optim_api.h"
 #include "kernels/topk_api.h"
+#include "optim/adamw_plan.h"
+#include "optim/bucket_hook.h"
 #include "runtime/arena.h"
 #include "runtime/engine.h"
 #include "runtime/mempool.h"
@@ -138,7 +140,21 @@ class EmuGroup {
     }
     p.scale = 1.0f;
     p.wait_ns = wait_ns_;
+    p.debug_checks = debug_checks_ ? 1 : 0;
     return p;
+  }
+  // Debug mode: every kernel verifies its buffer ranges and reports ERR_BOUNDS instead of touching
+  // memory outside them.
+  void set_debug_checks(bool on) { debug_checks_ = on; }
+  // Test hook: shrinks the capacity the kernels are told about (not the allocation), so that the
+  // range checks can be seen to fire without any out-of-range access.
+  void set_claimed_capacity(int64_t bytes) { claimed_capacity_ = bytes; }
+  // Fills all data buffers of every emulated rank's arena with a byte pattern (NaNs for 0xFF):
+  // a kernel that read a slot nobody wrote in the current epoch would then produce garbage.
+  void poison_buffers(int byte) {
+    for (int r = 0; r < ws_; ++r)
+      CK(cudaMemsetAsync(arena_->base(r) + kern::kSignalBytes, byte, kern::kNumParity * arena_->parity_bytes(),
+                         at::cuda::getCurrentCUDAStream()));
   }
   kern::LaunchCfg cfg(int ctas) {
     kern::LaunchCfg c;
@@ -184,19 +200,31 @@ class EmuGroup {
     check_fits(kern::twoshot_arena_bytes(static_cast<size_t>(p.count) * ws_ * kern::dtype_size(dt), ws_) + 128 * ws_);
     CK(kern::launch_reduce_scatter(p, dt, dt, cfg(ctas), at::cuda::getCurrentCUDAStream()));
   }
-  void allgather(std::vector<at::Tensor> outs, std::vector<at::Tensor> ins, int ctas) {
+  // pitch_bytes > 0: rank r's block lands at out + r * pitch_bytes (a slice of a larger gather)
+  void allgather(std::vector<at::Tensor> outs, std::vector<at::Tensor> ins, int ctas, int tile_bytes,
+                 int64_t pitch_bytes, int64_t slice_bytes, int64_t slice_offset) {
     c10::cuda::CUDAGuard g(ins[0].device());
     kern::CollParams p = params(ins, outs);
-    p.count = static_cast<int64_t>(ins[0].nbytes());
-    check_fits(static_cast<size_t>(p.count) + 16);
+    p.count = slice_bytes > 0 ? slice_bytes : static_cast<int64_t>(ins[0].nbytes());
+    p.out_pitch = pitch_bytes;
+    p.tile_bytes = tile_bytes;
+    if (slice_offset > 0)
+      for (int r = 0; r < ws_; ++r) {
+        p.ctx[r].in = static_cast<const char*>(p.ctx[r].in) + slice_offset;
+        p.ctx[r].out = static_cast<char*>(p.ctx[r].out) + slice_offset;
+      }
+    check_fits(kern::allgather_stage_bytes(static_cast<size_t>(p.count), ws_));
+    if (claimed_capacity_ > 0) p.parity_capacity = static_cast<size_t>(claimed_capacity_);
     CK(kern::launch_allgather(p, cfg(ctas), at::cuda::getCurrentCUDAStream()));
   }
-  void broadcast(std::vector<at::Tensor> ts, int root, int ctas) {
+  void broadcast(std::vector<at::Tensor> ts, int root, int ctas, int tile_bytes) {
     c10::cuda::CUDAGuard g(ts[0].device());
     kern::CollParams p = params(ts, ts);
     p.count = static_cast<int64_t>(ts[0].nbytes());
     p.root = root;
-    check_fits(static_cast<size_t>(p.count) + 16 * ws_);
+    p.tile_bytes = tile_bytes;
+    check_fits(kern::broadcast_stage_bytes(static_cast<size_t>(p.count)));
+    if (claimed_capacity_ > 0) p.parity_capacity = static_cast<size_t>(claimed_capacity_);
     CK(kern::launch_broadcast(p, cfg(ctas), at::cuda::getCurrentCUDAStream()));
   }
   void barrier() {
@@ -284,110 +312,9 @@ class EmuGroup {
   }
   int ws_;
   unsigned long long wait_ns_;
+  bool debug_checks_ = false;
+  int64_t claimed_capacity_ = 0;
   std::unique_ptr<SymmetricArena> arena_;
-};
-
-// Device-resident launch plan of the fused multi-tensor AdamW kernel.
-class AdamWPlan {
- public:
-  AdamWPlan(std::vector<at::Tensor> params, std::vector<at::Tensor> exp_avg, std::vector<at::Tensor> exp_avg_sq)
-      : params_(std::move(params)), m_(std::move(exp_avg)), v_(std::move(exp_avg_sq)) {
-    MCCL_CHECK_TENSOR(!params_.empty() && params_.size() == m_.size() && params_.size() == v_.size(),
-                      "AdamWPlan: list sizes differ");
-    std::vector<int64_t> ptr_p, ptr_m, ptr_v, sizes;
-    std::vector<int32_t> chunks;
-    for (size_t i = 0; i < params_.size(); ++i) {
-      for (const at::Tensor* t : {&params_[i], &m_[i], &v_[i]}) {
-        MCCL_CHECK_TENSOR(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous(),
-                          "AdamWPlan: float32 contiguous CUDA tensors only");
-        MCCL_CHECK_TENSOR(t->numel() == params_[i].numel() && t->device() == params_[0].device(),
-                          "AdamWPlan: shape/device mismatch");
-      }
-      ptr_p.push_back(reinterpret_cast<int64_t>(params_[i].data_ptr()));
-      ptr_m.push_back(reinterpret_cast<int64_t>(m_[i].data_ptr()));
-      ptr_v.push_back(reinterpret_cast<int64_t>(v_[i].data_ptr()));
-      const int64_t n = params_[i].numel();
-      sizes.push_back(n);
-      for (int64_t c = 0; c * kern::kAdamWChunk < n; ++c) {
-        chunks.push_back(static_cast<int32_t>(i));
-        chunks.push_back(static_cast<int32_t>(c));
-      }
-    }
-    auto dev = params_[0].device();
-    auto up64 = [&](const std::vector<int64_t>& v) {
-      return at::tensor(v, at::TensorOptions().dtype(at::kLong)).to(dev);
-    };
-    d_p_ = up64(ptr_p);
-    d_m_ = up64(ptr_m);
-    d_v_ = up64(ptr_v);
-    d_sizes_ = up64(sizes);
-    d_chunks_ = at::tensor(chunks, at::TensorOptions().dtype(at::kInt)).to(dev);
-    num_chunks_ = static_cast<int>(chunks.size() / 2);
-    grad_ptrs_.assign(params_.size(), 0);
-    d_g_ = at::zeros({static_cast<int64_t>(params_.size())}, at::TensorOptions().dtype(at::kLong).device(dev));
-  }
-
-  // grads[i] may move between steps (zero_grad(set_to_none=True)); the pointer
-  // table is re-uploaded only when an address changed.
-  void step(const std::vector<at::Tensor>& grads, double lr, double beta1, double beta2, double eps,
-            double weight_decay, int64_t step, double grad_scale) {
-    bind_grads(grads);
-    c10::cuda::CUDAGuard guard(params_[0].device());
-    launch(at::cuda::getCurrentCUDAStream(), lr, beta1, beta2, eps, weight_decay, step, grad_scale);
-  }
-
-  // Points the plan at `grads` (uploads the pointer table only when an address changed).
-  void bind_grads(const std::vector<at::Tensor>& grads) {
-    MCCL_CHECK_TENSOR(grads.size() == params_.size(), "AdamWPlan.step: expected one gradient per parameter");
-    bool changed = false;
-    for (size_t i = 0; i < grads.size(); ++i) {
-      const at::Tensor& g = grads[i];
-      MCCL_CHECK_TENSOR(g.is_cuda() && g.scalar_type() == at::kFloat && g.is_contiguous() &&
-                            g.numel() == params_[i].numel(),
-                        "AdamWPlan.step: gradient " << i << " must be a float32 contiguous CUDA tensor of the parameter's size");
-      int64_t a = reinterpret_cast<int64_t>(g.data_ptr());
-      if (a != grad_ptrs_[i]) {
-        grad_ptrs_[i] = a;
-        changed = true;
-      }
-    }
-    if (changed) {
-      c10::cuda::CUDAGuard guard(params_[0].device());
-      at::Tensor host = at::tensor(grad_ptrs_, at::TensorOptions().dtype(at::kLong));
-      d_g_.copy_(host);
-    }
-  }
-
-  void launch(cudaStream_t stream, double lr, double beta1, double beta2, double eps, double weight_decay,
-              int64_t step, double grad_scale) {
-    kern::AdamWTable tab;
-    tab.params = reinterpret_cast<const uint64_t*>(d_p_.data_ptr<int64_t>());
-    tab.grads = reinterpret_cast<const uint64_t*>(d_g_.data_ptr<int64_t>());
-    tab.exp_avg = reinterpret_cast<const uint64_t*>(d_m_.data_ptr<int64_t>());
-    tab.exp_avg_sq = reinterpret_cast<const uint64_t*>(d_v_.data_ptr<int64_t>());
-    tab.sizes = d_sizes_.data_ptr<int64_t>();
-    tab.chunks = reinterpret_cast<const int2*>(d_chunks_.data_ptr<int32_t>());
-    tab.num_chunks = num_chunks_;
-    kern::AdamWHyper h;
-    h.lr = static_cast<float>(lr);
-    h.beta1 = static_cast<float>(beta1);
-    h.beta2 = static_cast<float>(beta2);
-    h.eps = static_cast<float>(eps);
-    h.weight_decay = static_cast<float>(weight_decay);
-    const double bc1 = 1.0 - std::pow(beta1, static_cast<double>(step));
-    const double bc2 = 1.0 - std::pow(beta2, static_cast<double>(step));
-    h.step_size = static_cast<float>(lr / bc1);
-    h.inv_sqrt_bias2 = static_cast<float>(1.0 / std::sqrt(bc2));
-    h.grad_scale = static_cast<float>(grad_scale);
-    CK(kern::launch_adamw_multi(tab, h, stream));
-  }
-  int num_chunks() const { return num_chunks_; }
-
- private:
-  std::vector<at::Tensor> params_, m_, v_;
-  std::vector<int64_t> grad_ptrs_;
-  at::Tensor d_p_, d_g_, d_m_, d_v_, d_sizes_, d_chunks_;
-  int num_chunks_ = 0;
 };
 
 // (pairs as int32 [k,2], k) of the exact top-k of |grad + residual|; residual updated.
@@ -496,7 +423,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("lanes", &MCCLOptions::lanes)
       .def_readwrite("arena_bytes", &MCCLOptions::arena_bytes)
       .def_readwrite("device_wait_us", &MCCLOptions::device_wait_us)
-      .def_readwrite("blocking_wait", &MCCLOptions::blocking_wait);
+      .def_readwrite("blocking_wait", &MCCLOptions::blocking_wait)
+      .def_readwrite("nvls", &MCCLOptions::nvls)
+      .def_readwrite("nvls_bytes", &MCCLOptions::nvls_bytes)
+      .def_readwrite("nvls_min_bytes", &MCCLOptions::nvls_min_bytes)
+      .def_readwrite("nvls_split_min_bytes", &MCCLOptions::nvls_split_min_bytes)
+      .def_readwrite("tile_bytes", &MCCLOptions::tile_bytes)
+      .def_readwrite("debug_checks", &MCCLOptions::debug_checks);
 
   py::class_<ProcessGroupMCCL, c10::intrusive_ptr<ProcessGroupMCCL>>(m, "ProcessGroupMCCL", backend_cls)
       .def(py::init([](const c10::intrusive_ptr<c10d::Store>& store, int rank, int size,
@@ -523,20 +456,29 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("tensor"), py::arg("scale"), py::call_guard<py::gil_scoped_release>())
       .def("last_phase_stamps", &ProcessGroupMCCL::last_phase_stamps, py::call_guard<py::gil_scoped_release>())
       .def("allreduce_adamw",
-           [](ProcessGroupMCCL& pg, at::Tensor bucket, double scale, AdamWPlan& plan, std::vector<at::Tensor> grads,
-              double lr, double beta1, double beta2, double eps, double weight_decay, int64_t step) {
-             // bucket = sum(bucket) * scale in one kernel, then the bucket's AdamW update behind it on the
-             // same communication stream: no Python between the two, one Work covers both.
-             plan.bind_grads(grads);
+           [](ProcessGroupMCCL& pg, at::Tensor bucket, double scale, py::list specs, int64_t step) {
+             // bucket = sum(bucket) * scale in one kernel, then the bucket's AdamW update(s) behind it on the
+             // same communication stream: no Python between them, one Work covers all.  `specs` holds one
+             // (plan, grads, lr, beta1, beta2, eps, weight_decay) tuple per param group present in the bucket.
+             struct L {
+               AdamWPlan* plan;
+               double lr, b1, b2, eps, wd;
+             };
+             std::vector<L> ls;
+             for (auto item : specs) {
+               py::tuple t = item.cast<py::tuple>();
+               AdamWPlan* plan = t[0].cast<AdamWPlan*>();
+               plan->bind_grads(t[1].cast<std::vector<at::Tensor>>());
+               ls.push_back({plan, t[2].cast<double>(), t[3].cast<double>(), t[4].cast<double>(), t[5].cast<double>(),
+                             t[6].cast<double>()});
+             }
              std::vector<at::Tensor> v{bucket};
-             AdamWPlan* pl = &plan;
-             return pg.allreduce_scaled_then(v, static_cast<float>(scale), [=](cudaStream_t s) {
-               pl->launch(s, lr, beta1, beta2, eps, weight_decay, step, 1.0);
+             py::gil_scoped_release nogil;
+             return pg.allreduce_scaled_then(v, static_cast<float>(scale), [ls, step](cudaStream_t s) {
+               for (const auto& l : ls) l.plan->launch(s, l.lr, l.b1, l.b2, l.eps, l.wd, step, 1.0);
              });
            },
-           py::arg("bucket"), py::arg("scale"), py::arg("plan"), py::arg("grads"), py::arg("lr"), py::arg("beta1"),
-           py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("step"),
-           py::call_guard<py::gil_scoped_release>())
+           py::arg("bucket"), py::arg("scale"), py::arg("specs"), py::arg("step"))
       .def("_test_skip_next_launch", &ProcessGroupMCCL::test_skip_next_launch)
       .def("shutdown", &ProcessGroupMCCL::shutdown, py::call_guard<py::gil_scoped_release>());
 
@@ -685,7 +627,35 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("step", &AdamWPlan::step, py::arg("grads"), py::arg("lr"), py::arg("beta1"), py::arg("beta2"),
            py::arg("eps"), py::arg("weight_decay"), py::arg("step"), py::arg("grad_scale") = 1.0)
       .def_property_readonly("num_chunks", &AdamWPlan::num_chunks);
+  // ---- native DDP hook: allreduce + AdamW per bucket, registered on the C++ reducer ----
+  py::class_<BucketOptimizerState, std::shared_ptr<BucketOptimizerState>>(m, "BucketOptimizerState")
+      .def(py::init([](c10::intrusive_ptr<ProcessGroupMCCL> pg, double scale) {
+             return std::make_shared<BucketOptimizerState>(std::move(pg), scale);
+           }),
+           py::arg("backend"), py::arg("scale"))
+      .def("add_param", &BucketOptimizerState::add_param, py::arg("param"), py::arg("exp_avg"), py::arg("exp_avg_sq"),
+           py::arg("group"))
+      .def("set_hyper", &BucketOptimizerState::set_hyper, py::arg("group"), py::arg("lr"), py::arg("beta1"),
+           py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"))
+      .def("set_step", &BucketOptimizerState::set_step)
+      .def("take_stepped", &BucketOptimizerState::take_stepped);
+  m.def(
+      "_register_bucket_optimizer_hook",
+      [](py::object reducer, std::shared_ptr<BucketOptimizerState> st) {
+        auto r = reducer.cast<std::shared_ptr<c10d::Reducer>>();
+        r->register_comm_hook(std::make_unique<BucketOptimizerHook>(std::move(st)));
+      },
+      py::arg("reducer"), py::arg("state"),
+      "Installs the native allreduce+AdamW bucket hook on a DistributedDataParallel reducer (ddp.reducer).");
+
   m.def("_kernel_launches", []() { return kern::launch_counter().load(); });
+  // (tile_units, ntiles) the pipelined kernels derive for a 16-byte-unit index space and a grid
+  m.def("_tile_plan", [](int64_t units, int nctas, int nthreads, int64_t tile_bytes) {
+    int64_t tu = 0, nt = 0;
+    kern::tile_plan_host(units, nctas, nthreads, tile_bytes, &tu, &nt);
+    return std::make_pair(tu, nt);
+  }, py::arg("units"), py::arg("nctas"), py::arg("nthreads") = 512, py::arg("tile_bytes") = 0);
+  m.attr("MAX_CTAS_PER_LANE") = kern::kMaxCtasPerLane;
 
   // ---- top-k kernels ------------------------------------------------------------------------
   m.def("_topk_select", &topk_select, py::arg("grad"), py::arg("residual"), py::arg("ratio"));
@@ -700,8 +670,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("tiles") = 1, py::arg("push_gather") = false)
       .def("reduce_scatter", &EmuGroup::reduce_scatter, py::arg("outputs"), py::arg("inputs"),
            py::arg("op") = "sum", py::arg("ctas") = 0, py::arg("pitch") = 0)
-      .def("allgather", &EmuGroup::allgather, py::arg("outputs"), py::arg("inputs"), py::arg("ctas") = 0)
-      .def("broadcast", &EmuGroup::broadcast, py::arg("tensors"), py::arg("root"), py::arg("ctas") = 0)
+      .def("allgather", &EmuGroup::allgather, py::arg("outputs"), py::arg("inputs"), py::arg("ctas") = 0,
+           py::arg("tile_bytes") = 0, py::arg("pitch_bytes") = 0, py::arg("slice_bytes") = 0, py::arg("slice_offset") = 0)
+      .def("broadcast", &EmuGroup::broadcast, py::arg("tensors"), py::arg("root"), py::arg("ctas") = 0,
+           py::arg("tile_bytes") = 0)
+      .def("set_debug_checks", &EmuGroup::set_debug_checks)
+      .def("set_claimed_capacity", &EmuGroup::set_claimed_capacity)
+      .def("poison_buffers", &EmuGroup::poison_buffers, py::arg("byte") = 0xFF)
       .def("barrier", &EmuGroup::barrier)
       .def("barrier_with_absent_rank", &EmuGroup::barrier_with_absent_rank)
       .def("status", &EmuGroup::status)

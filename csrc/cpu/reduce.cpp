@@ -2,7 +2,9 @@
 
 #include <algorithm>
 #include <cmath>
+#include <limits>
 #include <thread>
+#include <type_traits>
 #include <vector>
 
 #include "common/errors.h"
@@ -34,6 +36,26 @@ void parallel_range(int64_t n, F&& body) {
   for (auto& t : th) t.join();
 }
 
+// MIN / MAX that give the same bits whichever operand comes first: a NaN on either side yields
+// the canonical quiet NaN (as torch and NCCL propagate it), and of +0 / -0 the minimum is -0 and
+// the maximum +0.  Two ranks that reduce the same pair in opposite orders therefore agree.
+template <typename A>
+inline A ordered_min(A x, A y) {
+  if constexpr (std::is_floating_point<A>::value) {
+    if (std::isnan(x) || std::isnan(y)) return std::numeric_limits<A>::quiet_NaN();
+    if (x == y) return std::signbit(x) ? x : y;
+  }
+  return y < x ? y : x;
+}
+template <typename A>
+inline A ordered_max(A x, A y) {
+  if constexpr (std::is_floating_point<A>::value) {
+    if (std::isnan(x) || std::isnan(y)) return std::numeric_limits<A>::quiet_NaN();
+    if (x == y) return std::signbit(x) ? y : x;
+  }
+  return y > x ? y : x;
+}
+
 template <typename T, typename Acc>
 void reduce_typed(T* d, const T* s, int64_t n, Op op) {
   parallel_range(n, [=](int64_t b, int64_t e) {
@@ -48,13 +70,13 @@ void reduce_typed(T* d, const T* s, int64_t n, Op op) {
       case Op::MIN:
         for (int64_t i = b; i < e; ++i) {
           Acc x = static_cast<Acc>(d[i]), y = static_cast<Acc>(s[i]);
-          d[i] = static_cast<T>(y < x ? y : x);
+          d[i] = static_cast<T>(ordered_min<Acc>(x, y));
         }
         break;
       case Op::MAX:
         for (int64_t i = b; i < e; ++i) {
           Acc x = static_cast<Acc>(d[i]), y = static_cast<Acc>(s[i]);
-          d[i] = static_cast<T>(y > x ? y : x);
+          d[i] = static_cast<T>(ordered_max<Acc>(x, y));
         }
         break;
       default:

@@ -13,7 +13,8 @@ namespace mccl {
 namespace kern {
 
 constexpr int kMaxWorld = 8;         // ranks sharing one NVSwitch domain
-constexpr int kMaxCtas = 128;        // upper bound on CTAs of one collective kernel
+constexpr int kMaxCtas = 128;        // upper bound on CTAs of one collective kernel (signal-pad rows)
+constexpr int kMaxCtasPerLane = 64;  // what a launcher may use: two lanes x 64 CTAs stay co-resident on 148 SMs
 constexpr int kNumPhases = 4;        // independent signal arrays per lane
 constexpr int kNumLanes = 2;         // collectives of consecutive epochs may run concurrently (one per lane)
 constexpr int kNumParity = 4;        // data buffers per arena: epoch e uses buffer e % 4
@@ -51,10 +52,12 @@ static_assert(kSigOffset + size_t(kNumLanes) * kNumPhases * kMaxCtas * kMaxWorld
 // word 0: 0 = healthy, else an ErrorCode; 1: seq; 2: phase; 3: peer waited for.
 enum ErrorCode : uint32_t { ERR_NONE = 0, ERR_WAIT_TIMEOUT = 1, ERR_BOUNDS = 2 };
 constexpr int kStatusWords = 8;
+constexpr int kStatusMirrorWord = 4;  // words 4-5: device address of a host-mapped copy of words 0-3 (0: none)
 // Phase stamps (ns, %globaltimer) of the last collective, written by CTA 0:
 // 0 kernel start, 1 entered, 2 push done, 3 peers' pushes seen, 4 reduce done,
 // 5 peers' reduces seen, 6 pull done / end.
 constexpr int kStampSlots = 8;
+constexpr int kMaxTilesPerCta = 1024;  // pipelined kernels publish a 12-bit running tile count
 
 struct RankCtx {
   int rank;
@@ -64,6 +67,12 @@ struct RankCtx {
   void* out;               // this rank's output (user tensor)
   uint32_t* status;        // kStatusWords words
   unsigned long long* stamps;  // optional: kStampSlots globaltimer stamps written by CTA 0 (nullptr = off)
+  // NVLS region (nullptr when the group has none): the same physical buffers of every rank, seen
+  // through this rank's own mapping (nvls_uc: plain loads/stores hit local memory only) and through
+  // the NVSwitch multicast mapping (nvls_mc: multimem.st reaches every rank's copy,
+  // multimem.ld_reduce returns the sum over all ranks' copies).
+  char* nvls_uc;
+  char* nvls_mc;
 };
 
 struct CollParams {
@@ -79,6 +88,13 @@ struct CollParams {
   int tiles;               // two-shot: pipeline tiles per CTA (<=1: bulk phases)
   int64_t chunk_pitch;     // reduce_scatter: elements between the starts of consecutive input chunks (0: count)
   int push_gather;         // two-shot allreduce: owners push reduced chunks (needs 2x arena) instead of peers pulling
+  int64_t out_pitch;       // allgather: bytes between the starts of consecutive ranks' blocks in `out` (0: count)
+  int tile_bytes;          // pipelined byte movers / NVLS kernels: bytes per pipeline tile (0: built-in default)
+  size_t nvls_offset;      // byte offset of this epoch's buffer inside the NVLS region
+  size_t nvls_capacity;    // bytes available in it
+  int use_nvls;            // byte movers: move the payload with multimem.st through the NVLS region
+  int debug_checks;        // verify every computed offset against the buffer bounds; a violation is
+                           // reported as ERR_BOUNDS in the status block and the access is skipped
 };
 
 struct LaunchCfg {
@@ -93,6 +109,11 @@ int pick_ctas(size_t bytes, int ws, int requested);
 // Arena-size requirements (bytes of one parity buffer) for a payload.
 size_t oneshot_arena_bytes(size_t nbytes, int ws);
 size_t twoshot_arena_bytes(size_t nbytes, int ws, bool push_gather = false);
+size_t allgather_stage_bytes(size_t nbytes_per_rank, int ws);  // staging space of one allgather launch
+size_t broadcast_stage_bytes(size_t nbytes);
+size_t nvls_allreduce_stage_bytes(size_t nbytes_wire, int ws);
+// Tile geometry the pipelined kernels derive for (units, grid); exposed for host-side checks.
+void tile_plan_host(int64_t units, int nctas, int nthreads, int64_t tile_bytes, int64_t* tile_units, int64_t* ntiles);
 
 // All launchers return cudaSuccess or the launch error; none synchronises.
 // dtype: element type of in/out.  wire: element type stored in the arena
@@ -108,6 +129,14 @@ cudaError_t launch_reduce_scatter(const CollParams& p, DType dtype, DType wire, 
 cudaError_t launch_allgather(const CollParams& p, LaunchCfg cfg, cudaStream_t s);
 cudaError_t launch_broadcast(const CollParams& p, LaunchCfg cfg, cudaStream_t s);
 cudaError_t launch_barrier(const CollParams& p, LaunchCfg cfg, cudaStream_t s);
+// SUM / AVG allreduce through the NVLS region (multimem.ld_reduce + multimem.st).  Supported
+// (dtype, wire): F32/F32, F16/F16, BF16/BF16, F32/BF16, F32/F16; anything else returns
+// cudaErrorNotSupported before launching.
+bool nvls_allreduce_supported(DType dtype, DType wire, int op);
+// `split`: the two local staging passes run as separate full-grid kernels around the kernel
+// that talks to the peers (large messages); otherwise one tile-pipelined kernel does all three.
+cudaError_t launch_allreduce_nvls(const CollParams& p, DType dtype, DType wire, LaunchCfg cfg, cudaStream_t s,
+                                  bool split = false);
 
 // ---- standalone elementwise kernels (test hooks + local paths) ---------------
 cudaError_t launch_ew_reduce(void* dst, const void* src, int64_t n, DType t, RedOp op, cudaStream_t s);

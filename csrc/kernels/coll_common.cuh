@@ -133,6 +133,101 @@ __device__ __forceinline__ bool wait_all(const CtaCtx& k, int phase, int only = 
   return __syncthreads_and(ok ? 1 : 0) != 0;
 }
 
+// Waits for the same CTA index of every rank whose bit is set in `mask`.
+__device__ __forceinline__ bool wait_mask(const CtaCtx& k, int phase, uint32_t mask, uint32_t count) {
+  const RankCtx& c = *k.c;
+  bool ok = true;
+  if (k.tid < c.ws && ((mask >> k.tid) & 1u))
+    ok = wait_epoch(sig_flag(c.arena[c.rank], lane_of(k.p->seq), phase, k.cta, k.tid), sig_value(k.p->seq, count), k.p->wait_ns, c.status,
+                    static_cast<uint32_t>(phase), static_cast<uint32_t>(k.tid));
+  return __syncthreads_and(ok ? 1 : 0) != 0;
+}
+
+// Debug-mode range check (CollParams::debug_checks): is [off, off + len) inside a buffer of `cap`
+// bytes?  A violation is recorded as ERR_BOUNDS {seq, site, rank} and the caller skips the kernel
+// body; nothing is accessed out of range and nothing traps.
+__device__ __forceinline__ bool range_ok(const CtaCtx& k, size_t off, size_t len, size_t cap, uint32_t site) {
+  if (!k.p->debug_checks) return true;
+  if (off <= cap && len <= cap - off) return true;
+  report_failure(k.c->status, ERR_BOUNDS, k.p->seq, site, static_cast<uint32_t>(k.c->rank));
+  return false;
+}
+
+// ---- NVSwitch multicast (NVLS) accesses --------------------------------------------------------
+// `multimem.st` stores 16 bytes to the same offset of every rank's buffer bound to the multicast
+// object; `multimem.ld_reduce` returns the element-wise sum over all ranks' copies, added up inside
+// the switch (16-bit floats are accumulated in fp32).  These are NVLS instructions on a multicast
+// *address*; they have nothing to do with TMA cluster multicast, which this library never uses.
+__device__ __forceinline__ void multimem_st16(void* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+template <typename W> struct MultimemSum;
+template <> struct MultimemSum<float> {
+  static __device__ __forceinline__ uint4 ld(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc)
+                 : "memory");
+    return v;
+  }
+};
+template <> struct MultimemSum<__half> {
+  static __device__ __forceinline__ uint4 ld(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc)
+                 : "memory");
+    return v;
+  }
+};
+template <> struct MultimemSum<__nv_bfloat16> {
+  static __device__ __forceinline__ uint4 ld(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc)
+                 : "memory");
+    return v;
+  }
+};
+
+// Tile geometry of the pipelined kernels.  The 16-byte-unit index space [0, units) is cut into
+// tiles of `tile_units` (a whole number of nthreads * kUnroll batches); tile g belongs to CTA
+// g % nctas on EVERY rank, so the CTA that wrote a tile on one rank is the CTA that reads it on
+// another and a CTA only ever waits for its own index on its peers.
+struct TilePlan {
+  int64_t units, tile_units, ntiles;
+  __host__ __device__ static TilePlan make(int64_t units, int nctas, int nthreads, int64_t tile_bytes) {
+    TilePlan t;
+    t.units = units;
+    const int64_t batch = static_cast<int64_t>(nthreads) * kUnroll;
+    const int64_t per_cta = (units + nctas - 1) / nctas;
+    int64_t want = (tile_bytes > 0 ? tile_bytes : (128 << 10)) / 16;
+    if (want > per_cta) want = per_cta;
+    int64_t tu = (want + batch - 1) / batch * batch;
+    const int64_t floor_tu = ((per_cta + kMaxTilesPerCta - 1) / kMaxTilesPerCta + batch - 1) / batch * batch;
+    if (tu < floor_tu) tu = floor_tu;
+    if (tu < batch) tu = batch;
+    t.tile_units = tu;
+    t.ntiles = (units + tu - 1) / tu;
+    return t;
+  }
+  __host__ __device__ int64_t count_for(int cta, int nctas) const {
+    return ntiles > cta ? (ntiles - cta + nctas - 1) / nctas : 0;
+  }
+  __host__ __device__ int64_t begin(int cta, int nctas, int64_t j) const {
+    return (static_cast<int64_t>(cta) + j * nctas) * tile_units;
+  }
+  __host__ __device__ int64_t end(int cta, int nctas, int64_t j) const {
+    const int64_t e = begin(cta, nctas, j) + tile_units;
+    return e < units ? e : units;
+  }
+};
+
 __device__ __forceinline__ void stamp(const CtaCtx& k, int slot) {
   if (k.c->stamps != nullptr && k.cta == 0 && k.tid == 0) k.c->stamps[slot] = globaltimer_ns();
 }
@@ -190,7 +285,9 @@ cudaError_t dispatch_types(DType dtype, DType wire, const CollParams& p, int cta
 
 int clamp_ctas(int ctas, const LaunchCfg& cfg) {
   if (ctas < 1) ctas = 1;
-  if (ctas > kMaxCtas) ctas = kMaxCtas;
+  // Two lanes may run at once and every CTA that waits on a peer must be resident: a request above
+  // the per-lane limit is clamped, not left to turn into a device-side wait timeout.
+  if (ctas > kMaxCtasPerLane) ctas = kMaxCtasPerLane;
   // Emulated ranks share one device and must all be co-resident.
   if (cfg.emulate_ranks > 0 && ctas > 16) ctas = 16;
   return ctas;

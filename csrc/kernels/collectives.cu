@@ -47,62 +47,120 @@ cudaError_t launch_reduce(int kind, const CollParams& p, DType dtype, DType wire
 }
 
 // ---------------------------------------------------------------------------
-// Byte movers: allgather (publish + pull), broadcast (root publishes, others
-// pull), barrier (flag exchange only).
+// Byte movers: allgather and broadcast.  Both PUSH: the sender loads each 16-byte unit of the
+// user tensor once and stores it into the staging buffer of every receiver (one plain store per
+// peer over NVLink, or ONE multimem.st through the NVSwitch multicast mapping when the group has
+// an NVLS region), publishes a running tile count, and the receiver copies finished tiles from
+// its own staging buffer into its output.  Stores are fire-and-forget, so the links run at their
+// store rate, and because the work is cut into tiles (TilePlan) the receiver's copy-out of tile
+// i overlaps the sender's push of tile i+1.  No rank ever stages its payload locally first.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void copy_bytes(const CtaCtx& k, char* dst, const char* src, int64_t nbytes) {
-  const bool al = is_aligned16(dst) && is_aligned16(src);
-  const int64_t units = (nbytes + 15) / 16;
-  const int64_t stride = static_cast<int64_t>(k.nctas) * k.nthreads;
-  const int64_t first = static_cast<int64_t>(k.cta) * k.nthreads + k.tid;
-  for (int64_t u0 = first; u0 < units; u0 += stride * kUnroll) {
-    uint4 v[kUnroll];
+constexpr int kDeep = 8;  // 16-byte loads in flight per thread in the local copy-out loops
+
+template <bool kMC>
+__device__ __forceinline__ char* stage_local(const CtaCtx& k) {
+  return kMC ? k.c->nvls_uc + k.p->nvls_offset : k.c->arena[k.c->rank] + k.p->parity_offset;
+}
+template <bool kMC>
+__device__ __forceinline__ size_t stage_capacity(const CtaCtx& k) {
+  return kMC ? k.p->nvls_capacity : k.p->parity_capacity;
+}
+// Stores one unit at byte `off` of the staging buffer of every rank in `mask` (never this rank's
+// own on the unicast path; the multicast store reaches all ranks, which is harmless).
+template <bool kMC>
+__device__ __forceinline__ void push16(const CtaCtx& k, size_t off, uint4 v, uint32_t mask) {
+  const RankCtx& c = *k.c;
+  if (kMC) {
+    multimem_st16(c.nvls_mc + k.p->nvls_offset + off, v);
+  } else {
+    for (int d = 1; d < c.ws; ++d) {
+      int q = c.rank + d;
+      if (q >= c.ws) q -= c.ws;
+      if ((mask >> q) & 1u) stg16(c.arena[q] + k.p->parity_offset + off, v);
+    }
+  }
+}
+// dst[u*16 ...] = staged units [u0, u1); `src` is unit-indexed from 0, dst holds nbytes bytes.
+__device__ __forceinline__ void copy_units_out(const CtaCtx& k, char* dst, const char* src, int64_t u0, int64_t u1,
+                                               int64_t nbytes) {
+  const bool al = is_aligned16(dst);
+  for (int64_t ub = u0; ub < u1; ub += static_cast<int64_t>(k.nthreads) * kDeep) {
+    uint4 v[kDeep];
 #pragma unroll
-    for (int i = 0; i < kUnroll; ++i) {
-      int64_t u = u0 + i * stride;
-      if (u < units)
-        v[i] = ld_vec_guarded<uint8_t>(reinterpret_cast<const uint8_t*>(src), u, nbytes, al);
+    for (int i = 0; i < kDeep; ++i) {
+      const int64_t u = ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
+      if (u < u1) v[i] = ldg16(src + u * 16);
     }
 #pragma unroll
-    for (int i = 0; i < kUnroll; ++i) {
-      int64_t u = u0 + i * stride;
-      if (u < units) st_vec_guarded<uint8_t>(reinterpret_cast<uint8_t*>(dst), u, nbytes, al, v[i]);
+    for (int i = 0; i < kDeep; ++i) {
+      const int64_t u = ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
+      if (u < u1) st_vec_guarded<uint8_t>(reinterpret_cast<uint8_t*>(dst), u, nbytes, al, v[i]);
     }
   }
 }
 
+// allgather: staging slot r of every rank receives rank r's block.
+template <bool kMC>
 __global__ void __launch_bounds__(512) allgather_kernel(const __grid_constant__ CollParams p) {
   CtaCtx k = make_ctx(p);
   const RankCtx& c = *k.c;
   if (!enter_collective(k)) return;
   const int64_t nbytes = p.count;
+  const int64_t pitch = p.out_pitch > 0 ? p.out_pitch : nbytes;
   const char* in = static_cast<const char*>(c.in);
   char* out = static_cast<char*>(c.out);
-  // publish my block in my own arena (the arena side is padded: whole units)
-  {
-    char* pub = c.arena[c.rank] + p.parity_offset;
-    const bool al = is_aligned16(in);
-    const int64_t units = (nbytes + 15) / 16;
-    const int64_t stride = static_cast<int64_t>(k.nctas) * k.nthreads;
-    for (int64_t u = static_cast<int64_t>(k.cta) * k.nthreads + k.tid; u < units; u += stride)
-      stg16(pub + u * 16, ld_vec_guarded<uint8_t>(reinterpret_cast<const uint8_t*>(in), u, nbytes, al));
-  }
-  signal_all(k, 0);
-  // own block needs no peer: copy it while the flags travel
-  if (out + static_cast<int64_t>(c.rank) * nbytes != in)
-    copy_bytes(k, out + static_cast<int64_t>(c.rank) * nbytes, in, nbytes);
-  if (!wait_all(k, 0)) return;
-  for (int d = 1; d < c.ws; ++d) {
-    int q = c.rank + d;
-    if (q >= c.ws) q -= c.ws;
-    copy_bytes(k, out + static_cast<int64_t>(q) * nbytes, c.arena[q] + p.parity_offset, nbytes);
+  const int64_t units = (nbytes + 15) / 16;
+  const size_t slot_bytes = round_up(static_cast<size_t>(units) * 16, 128);
+  if (!range_ok(k, 0, slot_bytes * c.ws, stage_capacity<kMC>(k), 10)) return;
+  const TilePlan tp = TilePlan::make(units, k.nctas, k.nthreads, p.tile_bytes);
+  const int64_t my_tiles = tp.count_for(k.cta, k.nctas);
+  const char* stage = stage_local<kMC>(k);
+  const bool in_al = is_aligned16(in);
+  char* own_out = out + static_cast<int64_t>(c.rank) * pitch;
+  const bool own_copy = own_out != in;  // in-place allgather: the own block is already there
+  const bool own_al = is_aligned16(own_out);
+  const uint32_t peers = ((1u << c.ws) - 1u) & ~(1u << c.rank);
+  for (int64_t it = 0; it <= my_tiles; ++it) {
+    if (it < my_tiles) {  // push tile `it` of my block
+      const int64_t u0 = tp.begin(k.cta, k.nctas, it), u1 = tp.end(k.cta, k.nctas, it);
+      for (int64_t ub = u0; ub < u1; ub += static_cast<int64_t>(k.nthreads) * kUnroll) {
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int i = 0; i < kUnroll; ++i) {
+          const int64_t u = ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
+          if (u < u1) v[i] = ld_vec_guarded<uint8_t>(reinterpret_cast<const uint8_t*>(in), u, nbytes, in_al);
+        }
+#pragma unroll
+        for (int i = 0; i < kUnroll; ++i) {
+          const int64_t u = ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
+          if (u < u1) {
+            push16<kMC>(k, c.rank * slot_bytes + static_cast<size_t>(u) * 16, v[i], peers);
+            if (own_copy) st_vec_guarded<uint8_t>(reinterpret_cast<uint8_t*>(own_out), u, nbytes, own_al, v[i]);
+          }
+        }
+      }
+      signal_all(k, 0, static_cast<uint32_t>(it + 1));
+    }
+    if (it >= 1) {  // copy tile it-1 of every peer's block out of my staging buffer
+      if (!wait_mask(k, 0, peers, static_cast<uint32_t>(it))) return;
+      const int64_t u0 = tp.begin(k.cta, k.nctas, it - 1), u1 = tp.end(k.cta, k.nctas, it - 1);
+      for (int d = 1; d < c.ws; ++d) {
+        int q = c.rank + d;
+        if (q >= c.ws) q -= c.ws;
+        copy_units_out(k, out + static_cast<int64_t>(q) * pitch, stage + q * slot_bytes, u0, u1, nbytes);
+      }
+    }
   }
 }
 
-// Broadcast in two hops so the root's egress is N, not (ws-1)*N: the root
-// publishes the payload; non-root rank r pulls slice r from the root, stores it
-// and republishes it in its own arena; every non-root then pulls the remaining
-// slices from the other non-roots (the root's own slice comes from the root).
+// broadcast.  Direct form (two ranks, small messages, or the NVLS path where one multimem.st
+// reaches everybody): the root pushes every tile to all receivers.  Two-hop form (unicast, large):
+// the message is cut into ws-1 slices, one per non-root; the root pushes slice s only to its
+// owner, which copies it out and forwards it to the other non-roots, so the root sends every byte
+// once and every link carries about N bytes in each direction.  The staging buffer is an image of
+// the message (unit U of the message at byte 16*U), tiles are cut in slice-local unit space and
+// belong to the same CTA index on every rank.
+template <bool kMC>
 __global__ void __launch_bounds__(512) broadcast_kernel(const __grid_constant__ CollParams p) {
   CtaCtx k = make_ctx(p);
   const RankCtx& c = *k.c;
@@ -111,51 +169,107 @@ __global__ void __launch_bounds__(512) broadcast_kernel(const __grid_constant__ 
   char* buf = static_cast<char*>(c.out);  // in-place tensor
   const int root = p.root;
   const int64_t units = (nbytes + 15) / 16;
-  const int64_t slice_units = (units + c.ws - 1) / c.ws;
-  const int64_t slice_bytes = slice_units * 16;
-  auto slice_len = [&](int s) -> int64_t {
-    int64_t b = static_cast<int64_t>(s) * slice_bytes, e = b + slice_bytes;
-    if (e > nbytes) e = nbytes;
-    return e > b ? e - b : 0;
-  };
-  if (c.rank == root) {
-    char* pub = c.arena[root] + p.parity_offset;
-    const bool al = is_aligned16(buf);
-    const int64_t stride = static_cast<int64_t>(k.nctas) * k.nthreads;
-    for (int64_t u = static_cast<int64_t>(k.cta) * k.nthreads + k.tid; u < units; u += stride)
-      stg16(pub + u * 16, ld_vec_guarded<uint8_t>(reinterpret_cast<const uint8_t*>(buf), u, nbytes, al));
-    signal_all(k, 0);
-    return;
-  }
-  if (!wait_all(k, 0, root)) return;
-  if (nbytes <= kBroadcastDirectBytes) {  // latency-bound: one hop straight from the root
-    copy_bytes(k, buf, c.arena[root] + p.parity_offset, nbytes);
-    return;
-  }
-  // hop 1: my slice, plus the root's slice, straight from the root
-  {
-    const char* rsrc = c.arena[root] + p.parity_offset;
-    char* mine = c.arena[c.rank] + p.parity_offset;
-    int64_t off = static_cast<int64_t>(c.rank) * slice_bytes;
-    int64_t len = slice_len(c.rank);
-    if (len > 0) {
-      copy_bytes(k, mine + off, rsrc + off, (len + 15) / 16 * 16);  // arena copy: whole units
-      copy_bytes(k, buf + off, rsrc + off, len);
+  if (!range_ok(k, 0, static_cast<size_t>(units) * 16, stage_capacity<kMC>(k), 20)) return;
+  const char* stage = stage_local<kMC>(k);
+  const uint32_t nonroot = ((1u << c.ws) - 1u) & ~(1u << root);
+  const bool buf_al = is_aligned16(buf);
+  const bool direct = kMC || c.ws == 2 || nbytes <= kBroadcastDirectBytes;
+  if (direct) {
+    const TilePlan tp = TilePlan::make(units, k.nctas, k.nthreads, p.tile_bytes);
+    const int64_t my_tiles = tp.count_for(k.cta, k.nctas);
+    for (int64_t it = 0; it < my_tiles; ++it) {
+      const int64_t u0 = tp.begin(k.cta, k.nctas, it), u1 = tp.end(k.cta, k.nctas, it);
+      if (c.rank == root) {
+        for (int64_t ub = u0; ub < u1; ub += static_cast<int64_t>(k.nthreads) * kUnroll) {
+          uint4 v[kUnroll];
+#pragma unroll
+          for (int i = 0; i < kUnroll; ++i) {
+            const int64_t u = ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
+            if (u < u1) v[i] = ld_vec_guarded<uint8_t>(reinterpret_cast<const uint8_t*>(buf), u, nbytes, buf_al);
+          }
+#pragma unroll
+          for (int i = 0; i < kUnroll; ++i) {
+            const int64_t u = ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
+            if (u < u1) push16<kMC>(k, static_cast<size_t>(u) * 16, v[i], nonroot);
+          }
+        }
+        signal_all(k, 0, static_cast<uint32_t>(it + 1));
+      } else {
+        if (!wait_mask(k, 0, 1u << root, static_cast<uint32_t>(it + 1))) return;
+        copy_units_out(k, buf, stage, u0, u1, nbytes);
+      }
     }
-    int64_t roff = static_cast<int64_t>(root) * slice_bytes;
-    int64_t rlen = slice_len(root);
-    if (rlen > 0) copy_bytes(k, buf + roff, rsrc + roff, rlen);
+    return;
   }
-  signal_all(k, 1);
-  // hop 2: the other non-roots' slices from their arenas
-  for (int d = 1; d < c.ws; ++d) {
-    int q = c.rank + d;
-    if (q >= c.ws) q -= c.ws;
-    if (q == root) continue;
-    if (!wait_all(k, 1, q)) return;
-    int64_t off = static_cast<int64_t>(q) * slice_bytes;
-    int64_t len = slice_len(q);
-    if (len > 0) copy_bytes(k, buf + off, c.arena[q] + p.parity_offset + off, len);
+  // ---- two hops ------------------------------------------------------------------------------
+  const int ns = c.ws - 1;
+  const int64_t slice_units = (units + ns - 1) / ns;
+  const TilePlan tp = TilePlan::make(slice_units, k.nctas, k.nthreads, p.tile_bytes);
+  const int64_t my_tiles = tp.count_for(k.cta, k.nctas);
+  auto slice_base = [&](int q) -> int64_t { return static_cast<int64_t>(q < root ? q : q - 1) * slice_units; };
+  if (c.rank == root) {
+    for (int64_t it = 0; it < my_tiles; ++it) {
+      const int64_t u0 = tp.begin(k.cta, k.nctas, it), u1 = tp.end(k.cta, k.nctas, it);
+      for (int d = 1; d < c.ws; ++d) {
+        int q = root + d;
+        if (q >= c.ws) q -= c.ws;
+        const int64_t base = slice_base(q);
+        char* dst = c.arena[q] + p.parity_offset;
+        for (int64_t ub = u0; ub < u1; ub += static_cast<int64_t>(k.nthreads) * kUnroll) {
+          uint4 v[kUnroll];
+#pragma unroll
+          for (int i = 0; i < kUnroll; ++i) {
+            const int64_t U = base + ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
+            if (U < base + u1 && U < units)
+              v[i] = ld_vec_guarded<uint8_t>(reinterpret_cast<const uint8_t*>(buf), U, nbytes, buf_al);
+          }
+#pragma unroll
+          for (int i = 0; i < kUnroll; ++i) {
+            const int64_t U = base + ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
+            if (U < base + u1 && U < units) stg16(dst + U * 16, v[i]);
+          }
+        }
+      }
+      signal_all(k, 0, static_cast<uint32_t>(it + 1));
+    }
+    return;
+  }
+  const int64_t my_base = slice_base(c.rank);
+  const uint32_t others = nonroot & ~(1u << c.rank);
+  for (int64_t it = 0; it <= my_tiles; ++it) {
+    if (it < my_tiles) {  // hop 1 arrived: keep tile `it` of my slice and forward it
+      if (!wait_mask(k, 0, 1u << root, static_cast<uint32_t>(it + 1))) return;
+      const int64_t u0 = tp.begin(k.cta, k.nctas, it), u1 = tp.end(k.cta, k.nctas, it);
+      for (int64_t ub = u0; ub < u1; ub += static_cast<int64_t>(k.nthreads) * kUnroll) {
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int i = 0; i < kUnroll; ++i) {
+          const int64_t U = my_base + ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
+          if (U < my_base + u1 && U < units) v[i] = ldg16(stage + U * 16);
+        }
+#pragma unroll
+        for (int i = 0; i < kUnroll; ++i) {
+          const int64_t U = my_base + ub + k.tid + static_cast<int64_t>(i) * k.nthreads;
+          if (U < my_base + u1 && U < units) {
+            push16<false>(k, static_cast<size_t>(U) * 16, v[i], others);
+            st_vec_guarded<uint8_t>(reinterpret_cast<uint8_t*>(buf), U, nbytes, buf_al, v[i]);
+          }
+        }
+      }
+      signal_all(k, 1, static_cast<uint32_t>(it + 1));
+    }
+    if (it >= 1 && others != 0u) {  // hop 2 arrived: tile it-1 of the other non-roots' slices
+      if (!wait_mask(k, 1, others, static_cast<uint32_t>(it))) return;
+      const int64_t u0 = tp.begin(k.cta, k.nctas, it - 1), u1 = tp.end(k.cta, k.nctas, it - 1);
+      for (int d = 1; d < c.ws; ++d) {
+        int q = c.rank + d;
+        if (q >= c.ws) q -= c.ws;
+        if (q == root) continue;
+        const int64_t base = slice_base(q);
+        const int64_t e = base + u1 < units ? base + u1 : units;
+        if (base + u0 < e) copy_units_out(k, buf, stage, base + u0, e, nbytes);
+      }
+    }
   }
 }
 
@@ -173,8 +287,8 @@ int pick_ctas(size_t bytes, int ws, int requested) {
   // (2 vectors per thread), up to the cap.  Small grids keep latency-bound
   // messages cheap, large ones are needed to fill NVLink.
   (void)ws;
-  int cap = requested > 0 ? requested : 128;
-  if (cap > kMaxCtas) cap = kMaxCtas;
+  int cap = requested > 0 ? requested : kMaxCtasPerLane;
+  if (cap > kMaxCtasPerLane) cap = kMaxCtasPerLane;
   size_t want = (bytes + (16u << 10) - 1) / (16u << 10);
   if (want < 1) want = 1;
   if (want > static_cast<size_t>(cap)) want = cap;
@@ -206,13 +320,32 @@ cudaError_t launch_reduce_scatter(const CollParams& p, DType dtype, DType wire, 
       cfg.ctas > 0 ? cfg.ctas : pick_ctas(p.count * dtype_size(wire) * p.ctx[0].ws, p.ctx[0].ws, 0), cfg);
   return launch_reduce(kReduceScatter, p, dtype, wire, ctas, cfg, s);
 }
+size_t allgather_stage_bytes(size_t nbytes_per_rank, int ws) {
+  return round_up(round_up(nbytes_per_rank, 16), 128) * ws;
+}
+size_t broadcast_stage_bytes(size_t nbytes) { return round_up(nbytes, 16); }
+
 cudaError_t launch_allgather(const CollParams& p, LaunchCfg cfg, cudaStream_t s) {
   int ctas = clamp_ctas(cfg.ctas > 0 ? cfg.ctas : pick_ctas(p.count * p.ctx[0].ws, p.ctx[0].ws, 0), cfg);
-  return do_launch(allgather_kernel, p, ctas, cfg.threads, cfg.emulate_ranks, s);
+  if (p.use_nvls) {
+    if (cfg.emulate_ranks > 0 || p.ctx[0].nvls_mc == nullptr) return cudaErrorInvalidValue;
+    return do_launch(allgather_kernel<true>, p, ctas, cfg.threads, 0, s);
+  }
+  return do_launch(allgather_kernel<false>, p, ctas, cfg.threads, cfg.emulate_ranks, s);
 }
 cudaError_t launch_broadcast(const CollParams& p, LaunchCfg cfg, cudaStream_t s) {
   int ctas = clamp_ctas(cfg.ctas > 0 ? cfg.ctas : pick_ctas(p.count, p.ctx[0].ws, 0), cfg);
-  return do_launch(broadcast_kernel, p, ctas, cfg.threads, cfg.emulate_ranks, s);
+  if (p.use_nvls) {
+    if (cfg.emulate_ranks > 0 || p.ctx[0].nvls_mc == nullptr) return cudaErrorInvalidValue;
+    return do_launch(broadcast_kernel<true>, p, ctas, cfg.threads, 0, s);
+  }
+  return do_launch(broadcast_kernel<false>, p, ctas, cfg.threads, cfg.emulate_ranks, s);
+}
+
+void tile_plan_host(int64_t units, int nctas, int nthreads, int64_t tile_bytes, int64_t* tile_units, int64_t* ntiles) {
+  const TilePlan t = TilePlan::make(units, nctas, nthreads, tile_bytes);
+  *tile_units = t.tile_units;
+  *ntiles = t.ntiles;
 }
 cudaError_t launch_barrier(const CollParams& p, LaunchCfg cfg, cudaStream_t s) {
   return do_launch(barrier_kernel, p, 1, 128, cfg.emulate_ranks, s);

@@ -69,6 +69,18 @@ __device__ __forceinline__ void report_failure(uint32_t* status, uint32_t code, 
     status[2] = phase;
     status[3] = peer;
     __threadfence();
+    // Words 4-5 hold the device address of a host-mapped mirror (0: none).  The first failure is
+    // copied there with plain stores, code last, so the host can see it without touching a stream.
+    const unsigned long long mirror = *reinterpret_cast<const unsigned long long*>(status + kStatusMirrorWord);
+    if (mirror != 0ull) {
+      volatile uint32_t* h = reinterpret_cast<volatile uint32_t*>(mirror);
+      h[1] = seq;
+      h[2] = phase;
+      h[3] = peer;
+      __threadfence_system();
+      h[0] = code;
+      __threadfence_system();
+    }
   }
 }
 

@@ -66,6 +66,30 @@ extern "C" __attribute__((visibility("default"))) int mccl_topk_select_noalloc(c
     std::snprintf(msg, sizeof(msg), "k = %lld is outside 1..n (n = %lld)", k, n);
     return fail(1, msg);
   }
+  // The scratch array that is used belongs to the CURRENT device, so the caller's buffers must
+  // live there too: a launch with another GPU's scratch would fail or, with peer access on,
+  // silently work on the wrong GPU's array.
+  {
+    int cur = -1;
+    cudaError_t ce = cudaGetDevice(&cur);
+    if (ce != cudaSuccess) return fail(2, cudaGetErrorString(ce));
+    const void* bufs[3] = {grad, residual, pairs_out};
+    const char* names[3] = {"grad", "residual", "pairs_out"};
+    for (int i = 0; i < 3; ++i) {
+      cudaPointerAttributes at;
+      ce = cudaPointerGetAttributes(&at, bufs[i]);
+      if (ce != cudaSuccess) {
+        cudaGetLastError();
+        return fail(2, cudaGetErrorString(ce));
+      }
+      if ((at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged) && at.device != cur) {
+        char msg[160];
+        std::snprintf(msg, sizeof(msg), "%s lives on device %d but device %d is current: make the buffers' device current",
+                      names[i], at.device, cur);
+        return fail(1, msg);
+      }
+    }
+  }
   void* scratch = nullptr;
   int rc = scratch_for_current_device(&scratch);
   if (rc != 0) return rc;

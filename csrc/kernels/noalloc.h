@@ -19,6 +19,9 @@
 // Rules for callers:
 //  * grad, residual and pairs_out are device pointers the caller owns:
 //    n floats, n floats (read and written) and k * 8 bytes.
+//  * The device that holds these buffers must be the current device of the calling thread
+//    (cudaSetDevice): each device has its own copy of the scratch array and the call uses the
+//    current device's.  Buffers on another device are rejected with code 1.
 //  * Limits: 1 <= k <= n <= MCCL_NOALLOC_TOPK_MAX_N.  Anything else is rejected
 //    with a non-zero return code and a message (mccl_noalloc_last_error()).
 //  * The first call on each device looks up the address of the scratch array

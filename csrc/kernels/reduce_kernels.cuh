@@ -214,6 +214,7 @@ __global__ void __launch_bounds__(512) twoshot_kernel(const __grid_constant__ Co
   }
   const int64_t total = kAllGather ? p.count : p.count * c.ws;
   const size_t slot_bytes = round_up(static_cast<size_t>(chunk_units) * 16, 128);
+  if (!range_ok(k, 0, slot_bytes * c.ws * (p.push_gather ? 2 : 1), p.parity_capacity, 50)) return;
   auto chunk_len = [&](int q) -> int64_t {  // valid elements of chunk q
     int64_t b = static_cast<int64_t>(q) * chunk_elems;
     int64_t e = b + chunk_elems;
@@ -345,11 +346,14 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const __grid_con
   using Acc = typename U::Acc;
   CtaCtx k = make_ctx(p);
   const RankCtx& c = *k.c;
+  stamp(k, 0);
   if (!enter_collective(k)) return;
+  stamp(k, 1);
 
   const int64_t n = p.count;
   const int64_t units = (n + U::N - 1) / U::N;
   const size_t slot_bytes = round_up(static_cast<size_t>(units) * 16, 128);
+  if (!range_ok(k, 0, slot_bytes * c.ws, p.parity_capacity, 40)) return;
   const T* in = static_cast<const T*>(c.in);
   const bool in_al = is_aligned16(in);
   const int64_t per = (units + k.nctas - 1) / k.nctas;
@@ -384,12 +388,16 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const __grid_con
       }
     }
   }
+  stamp(k, 2);
   signal_all(k, 0);
   if (!wait_all(k, 0)) return;
+  stamp(k, 3);
 
   char* local_buf = c.arena[c.rank] + p.parity_offset;
   if (u0 < u1)
     reduce_tile<T, W, kSum ? SUM : kRuntimeOp, CLS>(k, in, n, static_cast<T*>(c.out), u0, u1, slot_bytes, local_buf, false);
+  stamp(k, 4);
+  stamp(k, 6);
 }
 
 template <int CLS> struct ReduceClass {

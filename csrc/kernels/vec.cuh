@@ -79,19 +79,24 @@ template <> struct Traits<bool8> {
 // OP value meaning "MIN, MAX or PRODUCT chosen at run time" (see apply_rt).
 constexpr int kRuntimeOp = 100;
 
+// MIN / MAX propagate NaNs like torch and NCCL do (a comparison-only select would drop a NaN
+// depending on which side it is on).  For integer accumulators the tests fold away.
+template <typename A> __device__ __forceinline__ A nan_min(A a, A b) { return a != a ? a : (b != b ? b : (b < a ? b : a)); }
+template <typename A> __device__ __forceinline__ A nan_max(A a, A b) { return a != a ? a : (b != b ? b : (b > a ? b : a)); }
+
 template <typename T, int OP> struct Reduce {
   using Acc = typename Traits<T>::Acc;
   // Run-time choice among MIN / MAX / PRODUCT (the rarely used operators share
   // one kernel instantiation; SUM and AVG have their own fast one).
   static __device__ __forceinline__ Acc apply_rt(int op, Acc a, Acc b) {
-    const Acc mn = b < a ? b : a, mx = b > a ? b : a, pr = a * b;
+    const Acc mn = nan_min(a, b), mx = nan_max(a, b), pr = a * b;
     return op == MIN ? mn : op == MAX ? mx : pr;
   }
   static __device__ __forceinline__ Acc apply(Acc a, Acc b) {
     if (OP == SUM || OP == AVG) return a + b;
     if (OP == PRODUCT) return a * b;
-    if (OP == MIN) return b < a ? b : a;
-    return b > a ? b : a;
+    if (OP == MIN) return nan_min(a, b);
+    return nan_max(a, b);
   }
 };
 template <int OP> struct Reduce<bool8, OP> {

@@ -44,6 +44,22 @@ SymmetricArena::SymmetricArena(int rank, int world_size, size_t parity_bytes)
   MCCL_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&st), kern::kStatusWords * sizeof(uint32_t)));
   MCCL_CUDA_CHECK(cudaMemset(st, 0, kern::kStatusWords * sizeof(uint32_t)));
   status_.push_back(st);
+  // host-visible mirror of the first failure (optional: without it the status is still polled)
+  void* hp = nullptr;
+  if (cudaHostAlloc(&hp, kern::kStatusWords * sizeof(uint32_t), cudaHostAllocMapped) == cudaSuccess) {
+    std::memset(hp, 0, kern::kStatusWords * sizeof(uint32_t));
+    void* dp = nullptr;
+    if (cudaHostGetDevicePointer(&dp, hp, 0) == cudaSuccess) {
+      status_host_ = static_cast<volatile uint32_t*>(hp);
+      const unsigned long long addr = reinterpret_cast<unsigned long long>(dp);
+      MCCL_CUDA_CHECK(cudaMemcpy(st + kern::kStatusMirrorWord, &addr, sizeof(addr), cudaMemcpyHostToDevice));
+    } else {
+      cudaGetLastError();
+      cudaFreeHost(hp);
+    }
+  } else {
+    cudaGetLastError();
+  }
   MCCL_CUDA_CHECK(cudaDeviceSynchronize());
   if (ws_ == 1) ready_ = true;
 }
@@ -88,8 +104,9 @@ SymmetricArena::~SymmetricArena() {
   }
   for (auto* s : status_)
     if (s) cudaFree(s);
+  if (status_host_) cudaFreeHost(const_cast<uint32_t*>(status_host_));
   for (auto* s : stamps_)
-    if (s) cudaFree(s);
+    if (s) cudaFreeHost(s);
   if (prev >= 0) cudaSetDevice(prev);
 }
 
@@ -143,7 +160,11 @@ void SymmetricArena::fill_params(kern::CollParams& p, uint32_t epoch) const {
     c.ws = ws_;
     for (int r = 0; r < kern::kMaxWorld; ++r) c.arena[r] = r < ws_ ? bases_[r] : nullptr;
     c.status = status_[i];
-    c.stamps = (stamps_on_ && i < static_cast<int>(stamps_.size())) ? stamps_[i] : nullptr;
+    c.stamps = (stamps_on_ && i < static_cast<int>(stamps_dev_.size()))
+                   ? stamps_dev_[i] + static_cast<size_t>(epoch % kStampRing) * kern::kStampSlots
+                   : nullptr;
+    c.nvls_uc = nullptr;
+    c.nvls_mc = nullptr;
   }
 }
 
@@ -155,26 +176,36 @@ void SymmetricArena::read_status(uint32_t out[kern::kStatusWords], cudaStream_t 
 
 void SymmetricArena::enable_stamps(bool on) {
   if (on && stamps_.empty()) {
+    const size_t bytes = static_cast<size_t>(kStampRing) * kern::kStampSlots * sizeof(unsigned long long);
     for (size_t i = 0; i < status_.size(); ++i) {
-      unsigned long long* p = nullptr;
-      MCCL_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&p), kern::kStampSlots * sizeof(unsigned long long)));
-      MCCL_CUDA_CHECK(cudaMemset(p, 0, kern::kStampSlots * sizeof(unsigned long long)));
-      stamps_.push_back(p);
+      void* hp = nullptr;
+      void* dp = nullptr;
+      MCCL_CUDA_CHECK(cudaHostAlloc(&hp, bytes, cudaHostAllocMapped));
+      std::memset(hp, 0, bytes);
+      MCCL_CUDA_CHECK(cudaHostGetDevicePointer(&dp, hp, 0));
+      stamps_.push_back(static_cast<unsigned long long*>(hp));
+      stamps_dev_.push_back(static_cast<unsigned long long*>(dp));
     }
   }
   stamps_on_ = on;
 }
 
-void SymmetricArena::read_stamps(unsigned long long out[kern::kStampSlots], cudaStream_t stream, int r) const {
+void SymmetricArena::read_stamps(unsigned long long out[kern::kStampSlots], cudaStream_t stream, int r,
+                                 int64_t epoch) const {
+  (void)stream;
   for (int i = 0; i < kern::kStampSlots; ++i) out[i] = 0;
   if (stamps_.empty()) return;
-  MCCL_CUDA_CHECK(cudaMemcpyAsync(out, stamps_[emulated_ ? r : 0], kern::kStampSlots * sizeof(unsigned long long),
-                                  cudaMemcpyDeviceToHost, stream));
-  MCCL_CUDA_CHECK(cudaStreamSynchronize(stream));
+  const uint32_t e = epoch < 0 ? epoch_ : static_cast<uint32_t>(epoch);
+  const volatile unsigned long long* src =
+      stamps_[emulated_ ? r : 0] + static_cast<size_t>(e % kStampRing) * kern::kStampSlots;
+  for (int i = 0; i < kern::kStampSlots; ++i) out[i] = src[i];
 }
 
 void SymmetricArena::clear_status(cudaStream_t stream) {
-  for (auto* s : status_) MCCL_CUDA_CHECK(cudaMemsetAsync(s, 0, kern::kStatusWords * sizeof(uint32_t), stream));
+  // words 0-3 only: the mirror address in words 4-5 stays
+  for (auto* s : status_) MCCL_CUDA_CHECK(cudaMemsetAsync(s, 0, kern::kStatusMirrorWord * sizeof(uint32_t), stream));
+  if (status_host_)
+    for (int i = 0; i < kern::kStatusMirrorWord; ++i) status_host_[i] = 0u;
 }
 
 }  // namespace mccl

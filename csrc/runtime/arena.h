@@ -61,9 +61,17 @@ class SymmetricArena {
   // Copies the status block of rank r out (synchronous on `stream`).
   void read_status(uint32_t out[kern::kStatusWords], cudaStream_t stream, int r = 0) const;
   void clear_status(cudaStream_t stream);
+  // True once a kernel of this (real, non-emulated) arena has recorded a failure.  Reads a
+  // host-mapped mirror of the status block: no stream, no synchronisation, callable from any thread.
+  bool device_failed() const { return status_host_ != nullptr && status_host_[0] != 0u; }
   // Phase-stamp capture (off by default): fill_params passes the buffer to the kernels.
   void enable_stamps(bool on);
-  void read_stamps(unsigned long long out[kern::kStampSlots], cudaStream_t stream, int r = 0) const;
+  // Stamps of arena epoch `epoch` (default: the latest one).  The stamps live in host-mapped memory,
+  // one slot per epoch in a ring of kStampRing; the caller makes sure the kernel has finished.
+  void read_stamps(unsigned long long out[kern::kStampSlots], cudaStream_t stream, int r = 0,
+                   int64_t epoch = -1) const;
+  bool stamps_enabled() const { return stamps_on_; }
+  static constexpr int kStampRing = 64;
   char* base(int r) const { return bases_[r]; }
 
  private:
@@ -78,7 +86,9 @@ class SymmetricArena {
   std::vector<char*> bases_;       // [ws]; bases_[rank_] is the local allocation
   std::vector<bool> opened_;       // peers mapped through IPC (to close)
   std::vector<uint32_t*> status_;  // device status blocks (1 real, ws emulated)
-  std::vector<unsigned long long*> stamps_;
+  volatile uint32_t* status_host_ = nullptr;  // pinned, device-mapped mirror of status_[0][0..3] (real arenas)
+  std::vector<unsigned long long*> stamps_;      // host addresses of the pinned stamp rings
+  std::vector<unsigned long long*> stamps_dev_;  // the same memory as the device sees it
   bool stamps_on_ = false;
 };
 

@@ -36,6 +36,21 @@ def _load_native():
     """Imports ``_C``; builds it first when the library is missing (source checkout)."""
     global _native_error
     import torch.distributed  # noqa: F401  (registers the c10d pybind base classes)
+    alt = os.environ.get("MCCL_NATIVE_LIB", "")
+    if alt:
+        # An explicitly named build of the extension (the sanitizer-instrumented one, for instance).
+        import importlib.machinery
+        import importlib.util
+        try:
+            loader = importlib.machinery.ExtensionFileLoader(__name__ + "._C", alt)
+            spec = importlib.util.spec_from_file_location(__name__ + "._C", alt, loader=loader)
+            mod = importlib.util.module_from_spec(spec)
+            loader.exec_module(mod)
+            sys.modules[__name__ + "._C"] = mod
+            return mod
+        except Exception as e:
+            _native_error = e
+            return None
     try:
         from . import _C  # type: ignore[attr-defined]
         return _C

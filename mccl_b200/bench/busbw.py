@@ -9,13 +9,18 @@ Method (as in NCCL-tests and the reference's tests/bench_busbw.py:57-137):
 for reduce_scatter/allgather (bytes = the full gathered size) and 1 for broadcast.
 Timing: CUDA events around `iters` back-to-back calls after warm-up, max over ranks.
 Buffers rotate through a pool larger than the 126 MB L2, so no iteration finds its input
-in cache.  Run it with ``MCCL_ALGO=oneshot`` and ``MCCL_ALGO=twoshot`` to find the crossover
-that goes into a tuner file, or let ``--tune FILE`` measure it (one-shot and two-shot pinned through
-``MCCLOptions`` on two extra groups) and write the file for ``MCCL_TUNE_FILE``; ``MCCL_COMM_CTAS`` sizes the grid.
+in cache.
+
+``--variants oneshot,twoshot,nvls`` adds one extra mccl process group per name with the kernel
+variant pinned through ``MCCLOptions`` (the default group keeps the tuner's choice), so one run
+shows every variant next to NCCL.  ``--tune FILE`` measures the crossovers for every op and both
+element classes on this world size and writes the file ``MCCL_TUNE_FILE`` loads.  ``--overlap``
+measures communication / compute overlap at a 25 MB bucket (reference tests/bench_busbw.py:69-137).
 """
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import sys
@@ -86,59 +91,184 @@ def time_calls(calls, iters, warmup, dev, sync_group):
     return float(t.item())
 
 
-def tune(path, rank, ws, dev):
-    """Finds the one-shot / two-shot crossover for this world size and writes a tuner file.
-
-    Two extra process groups are created with the variant pinned through ``MCCLOptions``
-    (``pg_options`` are honoured by the backend); fp32 allreduce is timed from 16 KiB to
-    64 MiB and the largest size at which one-shot is at least as fast becomes
-    ``ws<N>_oneshot_max_bytes``.  The two forms of the two-shot second half (peers pull the
-    reduced chunks / owners push them) are then timed at 32 and 64 MiB; ``ws<N>_push_gather``
-    is 1 when pushing wins at both.  Load the result with ``MCCL_TUNE_FILE`` on every rank.
-    """
-    import datetime
-
+def pinned_group(algo=None, gather=None, nvls=None):
+    """An extra mccl process group whose kernel variant is pinned through ``MCCLOptions``."""
     from mccl_b200 import _C
-    groups = {}
-    for algo in ("oneshot", "twoshot"):
-        o = _C.MCCLOptions(datetime.timedelta(seconds=120))
+    o = _C.MCCLOptions(datetime.timedelta(seconds=120))
+    if algo is not None:
         o.algo = algo
-        groups[algo] = dist.new_group(backend="mccl", pg_options=o)
-    best, rows, size = 0, [], 16 << 10
-    while size <= (64 << 20):
-        numel = size // 4
-        t = {}
-        for algo, g in groups.items():
-            calls, _ = make_call("allreduce", g, ws, rank, numel, torch.float32, dev, pool=8)
-            t[algo] = time_calls(calls, 40, 5, dev, None)
-        rows.append({"bytes": size, "oneshot_us": round(t["oneshot"] * 1e3, 2), "twoshot_us": round(t["twoshot"] * 1e3, 2)})
-        if t["oneshot"] <= t["twoshot"]:
-            best = size
-        if rank == 0:
-            print(json.dumps(rows[-1]), flush=True)
-        size *= 2
-    gather_groups = {}
-    for mode in ("pull", "push"):
-        o = _C.MCCLOptions(datetime.timedelta(seconds=120))
-        o.algo = "twoshot"
-        o.gather = mode
-        gather_groups[mode] = dist.new_group(backend="mccl", pg_options=o)
-    push_wins, gather_rows = 0, []
+    if gather is not None:
+        o.gather = gather
+    if nvls is not None:
+        o.nvls = nvls
+    return dist.new_group(backend="mccl", pg_options=o)
+
+
+def has_nvls(group, dev):
+    import mccl_b200 as mccl
+    dist.all_reduce(torch.ones(8, device=dev), group=group)
+    return mccl.get_backend(group=group, device=dev).data_plane().endswith("+nvls")
+
+
+def pool_and_iters(nbytes, quick=False):
+    pool = max(1, min(16, (2 * L2_BYTES) // max(nbytes, 1)))
+    if nbytes >= L2_BYTES:
+        pool = 2 if nbytes <= (256 << 20) else 1
+    iters = 200 if nbytes <= (1 << 20) else 50 if nbytes <= (64 << 20) else 10
+    if quick:
+        iters = max(iters // 4, 5)
+    return pool, iters
+
+
+def tune(path, rank, ws, dev, max_bytes):
+    """Measures, for this world size, every choice the tuner table holds and writes a tuner file.
+
+    allreduce (fp32 and bf16): one-shot, two-shot and, where the box has it, NVLS kernels pinned on
+    three groups and timed from 16 KiB to ``max_bytes``; ``oneshot_max_bytes`` is the largest size
+    up to which one-shot is never beaten, ``nvls_min_bytes`` the smallest size from which NVLS is
+    never beaten by two-shot.  allgather / broadcast: plain peer stores vs ``multimem.st``.
+    The two forms of the two-shot second half (peers pull / owners push) are timed at 32 and
+    64 MiB.  Load the result with ``MCCL_TUNE_FILE`` on every rank.
+    """
+    groups = {"oneshot": pinned_group("oneshot", nvls="0"), "twoshot": pinned_group("twoshot", nvls="0")}
+    nv = pinned_group("nvls", nvls="1")
+    nvls = has_nvls(nv, dev)
+    if nvls:
+        groups["nvls"] = nv
+    table, measured = {}, []
+    sizes = []
+    b = 16 << 10
+    while b <= max_bytes:
+        sizes.append(b)
+        b *= 2
+    for dname, key in (("fp32", ""), ("bf16", "_16bit")):
+        dtype = DTYPES[dname]
+        esz = 4 if dname == "fp32" else 2
+        t_all = {}
+        for size in sizes:
+            pool, iters = pool_and_iters(size, quick=True)
+            t = {}
+            for algo, g in groups.items():
+                if algo == "oneshot" and size * ws > (128 << 20):
+                    continue  # needs ws slots of the whole vector in one arena buffer
+                calls, _ = make_call("allreduce", g, ws, rank, size // esz, dtype, dev, pool)
+                t[algo] = time_calls(calls, iters, 3, dev, None)
+                del calls
+            t_all[size] = t
+            row = {"op": "allreduce", "dtype": dname, "bytes": size, **{k + "_us": round(v * 1e3, 2) for k, v in t.items()}}
+            measured.append(row)
+            if rank == 0:
+                print(json.dumps(row), flush=True)
+            torch.cuda.empty_cache()
+        best_one = 0
+        for size in sizes:
+            t = t_all[size]
+            if "oneshot" in t and t["oneshot"] <= min(v for k, v in t.items() if k != "oneshot"):
+                best_one = size
+            else:
+                break
+        table[f"ws{ws}_oneshot_max_bytes{key}"] = best_one
+        nvls_min = -1
+        if nvls:
+            for size in reversed(sizes):
+                t = t_all[size]
+                if t["nvls"] <= t["twoshot"]:
+                    nvls_min = size
+                else:
+                    break
+            if nvls_min >= 0:
+                nvls_min = max(nvls_min, best_one + 1)
+        table[f"ws{ws}_nvls_min_bytes{key}"] = nvls_min
+    if nvls:
+        for op, field in (("allgather", "allgather_nvls_min_bytes"), ("broadcast", "broadcast_nvls_min_bytes")):
+            t_all = {}
+            for size in sizes:
+                pool, iters = pool_and_iters(size, quick=True)
+                t = {}
+                for name, g in (("unicast", groups["twoshot"]), ("nvls", nv)):
+                    calls, _ = make_call(op, g, ws, rank, size // 4, torch.float32, dev, pool)
+                    t[name] = time_calls(calls, iters, 3, dev, None)
+                    del calls
+                t_all[size] = t
+                row = {"op": op, "bytes": size, **{k + "_us": round(v * 1e3, 2) for k, v in t.items()}}
+                measured.append(row)
+                if rank == 0:
+                    print(json.dumps(row), flush=True)
+                torch.cuda.empty_cache()
+            m = -1
+            for size in reversed(sizes):
+                if t_all[size]["nvls"] <= t_all[size]["unicast"]:
+                    # allgather's threshold is per-rank bytes
+                    m = size // ws if op == "allgather" else size
+                else:
+                    break
+            table[f"ws{ws}_{field}"] = m
+    gather_groups = {"pull": pinned_group("twoshot", "pull", "0"), "push": pinned_group("twoshot", "push", "0")}
+    push_wins = 0
     for size in (32 << 20, 64 << 20):
         t = {}
         for mode, g in gather_groups.items():
             calls, _ = make_call("allreduce", g, ws, rank, size // 4, torch.float32, dev, pool=4)
             t[mode] = time_calls(calls, 20, 5, dev, None)
-        gather_rows.append({"bytes": size, "pull_us": round(t["pull"] * 1e3, 2), "push_us": round(t["push"] * 1e3, 2)})
+            del calls
+        row = {"op": "allreduce-twoshot-gather", "bytes": size, "pull_us": round(t["pull"] * 1e3, 2), "push_us": round(t["push"] * 1e3, 2)}
+        measured.append(row)
         push_wins += t["push"] < t["pull"]
         if rank == 0:
-            print(json.dumps(gather_rows[-1]), flush=True)
-    push = int(push_wins == 2)
+            print(json.dumps(row), flush=True)
+    table[f"ws{ws}_push_gather"] = int(push_wins == 2)
     if rank == 0:
         with open(path, "w") as f:
-            json.dump({f"ws{ws}_oneshot_max_bytes": best, f"ws{ws}_push_gather": push, "measured": rows,
-                       "measured_gather": gather_rows}, f, indent=1)
-        print(f"wrote {path}: ws{ws}_oneshot_max_bytes = {best}, ws{ws}_push_gather = {push}", flush=True)
+            json.dump({**table, "measured": measured}, f, indent=1)
+        print(f"wrote {path}: {json.dumps(table)}", flush=True)
+
+
+def overlap(rank, ws, dev, bucket_bytes=25 << 20, iters=30):
+    """Communication / compute overlap at one DDP-bucket size.
+
+    Times `iters` allreduces alone, `iters` matmul chains alone and both together (async allreduce
+    issued first, then the chain, then wait), on the device, max over ranks.  Efficiency is
+    (serial - together) / (serial - max(comm, compute)): 1.0 = the shorter one is hidden completely.
+    """
+    t = torch.randn(bucket_bytes // 4, device=dev)
+    a = torch.randn(4096, 4096, device=dev)
+
+    def chain():
+        b = a
+        for _ in range(8):
+            b = b @ a
+        return b
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        v = torch.tensor([s.elapsed_time(e) / iters], dtype=torch.float64, device=dev)
+        dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        return float(v.item())
+
+    def both():
+        w = dist.all_reduce(t, async_op=True)
+        chain()
+        w.wait()
+
+    comm = timed(lambda: dist.all_reduce(t))
+    comp = timed(chain)
+    tog = timed(both)
+    serial, ideal = comm + comp, max(comm, comp)
+    row = {"op": "overlap", "bucket_bytes": bucket_bytes, "n_gpus": ws, "comm_ms": round(comm, 4), "compute_ms": round(comp, 4),
+           "together_ms": round(tog, 4), "overlap_efficiency": round((serial - tog) / max(serial - ideal, 1e-9), 3)}
+    if rank == 0:
+        print(json.dumps(row), flush=True)
+    return row
 
 
 def main(argv=None):
@@ -148,9 +278,12 @@ def main(argv=None):
     ap.add_argument("--min-bytes", type=int, default=1024)
     ap.add_argument("--max-bytes", type=int, default=1 << 30)
     ap.add_argument("--compare-nccl", action="store_true")
+    ap.add_argument("--variants", default="", help="comma list of oneshot,twoshot,nvls: extra groups with the variant pinned")
     ap.add_argument("--out", default="")
     ap.add_argument("--quick", action="store_true", help="every other size, fewer iterations")
-    ap.add_argument("--tune", default="", help="measure one-shot vs two-shot allreduce and write a tuner file here")
+    ap.add_argument("--tune", default="", help="measure every tuner crossover on this world size and write a tuner file here")
+    ap.add_argument("--tune-max-bytes", type=int, default=256 << 20)
+    ap.add_argument("--overlap", action="store_true", help="also measure comm/compute overlap at a 25 MB bucket")
     args = ap.parse_args(argv)
 
     import mccl_b200 as mccl  # noqa: F401  (registers the backend)
@@ -162,10 +295,17 @@ def main(argv=None):
     dev = torch.device("cuda", local)
     dist.init_process_group("mccl", rank=rank, world_size=ws, device_id=dev)
     if args.tune:
-        tune(args.tune, rank, ws, dev)
+        tune(args.tune, rank, ws, dev, args.tune_max_bytes)
         dist.destroy_process_group()
         return 0
     groups = {"mccl": None}
+    for v in [x for x in args.variants.split(",") if x]:
+        g = pinned_group(v, nvls="1" if v == "nvls" else "0")
+        if v == "nvls" and not has_nvls(g, dev):
+            if rank == 0:
+                print(json.dumps({"note": "no NVLS on this box: variant skipped"}), flush=True)
+            continue
+        groups["mccl-" + v] = g
     if args.compare_nccl:
         groups["nccl"] = dist.new_group(backend="nccl")
     sizes = []
@@ -174,19 +314,20 @@ def main(argv=None):
         sizes.append(b)
         b *= 4 if args.quick else 2
     rows = []
-    for op in args.ops.split(","):
+    if rank == 0:
+        print(json.dumps({"data_plane": mccl.get_backend(device=dev).data_plane() if ws > 1 else "local", "n_gpus": ws}), flush=True)
+    for op in [o for o in args.ops.split(",") if o]:
         for dname in args.dtypes.split(","):
             dtype = DTYPES[dname]
             esz = torch.empty(0, dtype=dtype).element_size()
             for nbytes_req in sizes:
                 numel = max(nbytes_req // esz, 1)
-                pool = max(1, min(16, (2 * L2_BYTES) // max(nbytes_req, 1)))
-                if nbytes_req >= L2_BYTES:
-                    pool = 2 if nbytes_req <= (256 << 20) else 1
-                iters = 200 if nbytes_req <= (1 << 20) else 50 if nbytes_req <= (64 << 20) else 10
-                if args.quick:
-                    iters = max(iters // 4, 5)
+                pool, iters = pool_and_iters(nbytes_req, args.quick)
                 for gname, group in groups.items():
+                    if gname == "mccl-oneshot" and (op != "allreduce" or nbytes_req * ws > (128 << 20)):
+                        continue
+                    if gname == "mccl-twoshot" and op == "reduce_scatter":
+                        continue  # reduce_scatter has one kernel: same as the default group
                     calls, nbytes = make_call(op, group, ws, rank, numel, dtype, dev, pool)
                     ms = time_calls(calls, iters, max(3, iters // 10), dev, groups["mccl"])
                     algbw = nbytes / (ms * 1e-3) / 1e9
@@ -198,6 +339,8 @@ def main(argv=None):
                         print(json.dumps(row), flush=True)
                     del calls
                 torch.cuda.empty_cache()
+    if args.overlap:
+        rows.append(overlap(rank, ws, dev))
     if rank == 0 and args.out:
         with open(args.out, "w") as f:
             for r in rows:

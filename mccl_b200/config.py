@@ -81,9 +81,9 @@ _FIELD_SPEC: Dict[str, tuple] = {
     "max_queue_depth": ("MCCL_MAX_QUEUE_DEPTH", _in_range(1, None), "host"),
     "log_level": ("MCCL_LOG_LEVEL", _log_level, "both"),
     # B200 data plane
-    "algo": ("MCCL_ALGO", _one_of("auto", "oneshot", "twoshot", "staged"), "cuda"),
+    "algo": ("MCCL_ALGO", _one_of("auto", "oneshot", "twoshot", "nvls", "staged"), "cuda"),
     "oneshot_max_bytes": ("MCCL_ONESHOT_MAX_BYTES", _in_range(-1, None), "cuda"),
-    "comm_ctas": ("MCCL_COMM_CTAS", _in_range(0, 128), "cuda"),
+    "comm_ctas": ("MCCL_COMM_CTAS", _in_range(0, 64), "cuda"),
     "wire_dtype": ("MCCL_WIRE_DTYPE", _one_of("none", "bf16", "fp16"), "cuda"),
     "tune_file": ("MCCL_TUNE_FILE", None, "cuda"),
     "device_wait_us": ("MCCL_DEVICE_WAIT_US", _in_range(1, None), "cuda"),
@@ -93,6 +93,12 @@ _FIELD_SPEC: Dict[str, tuple] = {
     "tiles": ("MCCL_TILES", _in_range(1, 64), "cuda"),
     "segment_bytes": ("MCCL_SEGMENT_BYTES", _in_range(1 << 20, None), "cuda"),
     "device_timing": ("MCCL_DEVICE_TIMING", _in_range(0, None), "cuda"),
+    "nvls": ("MCCL_NVLS", _one_of("auto", "0", "1", "on", "off"), "cuda"),
+    "nvls_bytes": ("MCCL_NVLS_BYTES", _in_range(1 << 20, None), "cuda"),
+    "nvls_min_bytes": ("MCCL_NVLS_MIN_BYTES", _in_range(-2, None), "cuda"),
+    "nvls_split_min_bytes": ("MCCL_NVLS_SPLIT_MIN_BYTES", _in_range(-2, None), "cuda"),
+    "tile_bytes": ("MCCL_TILE_BYTES", _in_range(0, None), "cuda"),
+    "debug_checks": ("MCCL_DEBUG_CHECKS", None, "cuda"),
     # integration hint only (never exported)
     "ddp_bucket_mb": (None, _in_range(1, None), "both"),
 }
@@ -150,6 +156,12 @@ class MCCLConfig:
     tiles: int = 1                  # two-shot pipeline tiles per CTA
     segment_bytes: int = 64 * 1024 * 1024   # large allreduces run as segments of this size on alternating lanes
     device_timing: int = 8          # every Nth CUDA collective is device-timed for the metrics (0: never)
+    nvls: str = "auto"              # NVLink multicast (in-switch reduction): auto | 0 | 1
+    nvls_bytes: int = 64 * 1024 * 1024      # one of the four NVLS buffers per rank
+    nvls_min_bytes: int = -2        # allreduce: smallest payload for the NVLS kernel (-2: tuner table, -1: never)
+    nvls_split_min_bytes: int = -2  # NVLS allreduce: staging passes as separate kernels from this size (-2: tuner, -1: never)
+    tile_bytes: int = 0             # pipeline tile of the byte movers and NVLS kernels (0: tuner table)
+    debug_checks: bool = False      # kernels verify their buffer ranges and report violations instead of accessing
     # integration hint (not exported to the native layer)
     ddp_bucket_mb: int = 25
 
@@ -159,7 +171,7 @@ class MCCLConfig:
     # native default differs (ephemeral ports) or derives from other knobs.
     _EXPORT_ONLY_IF_CHANGED = ("port_base", "device_wait_us", "oneshot_max_bytes", "comm_ctas",
                                "arena_bytes", "blocking_wait", "algo", "wire_dtype", "gather", "tiles", "segment_bytes",
-                               "device_timing")
+                               "device_timing", "nvls", "nvls_bytes", "nvls_min_bytes", "nvls_split_min_bytes", "tile_bytes", "debug_checks")
 
     def __post_init__(self) -> None:
         self._ENV_MAP = {env: name for name, (env, _v, _s) in _FIELD_SPEC.items() if env}

@@ -103,16 +103,37 @@ def optimizer_in_backward_hook(state: OptimizerInBackward, bucket: dist.GradBuck
     opt = state.optimizer
     if bucket.index() == 0:
         opt.begin_step_in_backward()
-    plan, group, own = opt.bucket_plan(bucket.index(), bucket.parameters())
-    b1, b2 = group["betas"]
-    work = backend.allreduce_adamw(buf, state.scale, plan, bucket.gradients(), group["lr"], b1, b2, group["eps"],
-                                   group["weight_decay"], opt._bw_step)
-    opt.mark_bucket_stepped(own)
+    plans = opt.bucket_plans(bucket.index(), bucket.parameters())
+    grads = bucket.gradients()
+    specs = []
+    for plan, group, own, pos in plans:
+        b1, b2 = group["betas"]
+        specs.append((plan, [grads[i] for i in pos], group["lr"], b1, b2, group["eps"], group["weight_decay"]))
+        opt.mark_bucket_stepped(own)
+    work = backend.allreduce_adamw(buf, state.scale, specs, opt._bw_step)
     return work.get_future().then(_first_tensor)
 
 
 def _first_tensor(fut):
     return fut.value()[0]
+
+
+def _install_native_bucket_hook(ddp, optimizer, process_group) -> None:
+    """Registers the C++ allreduce+AdamW hook on DDP's reducer (no Python per bucket).
+
+    The optimizer's state is created up front and handed to the hook; a forward pre-hook pushes the
+    current hyper-parameters and step number before every iteration.
+    """
+    from .. import require_native
+
+    native = require_native()
+    device = next(ddp.module.parameters()).device
+    backend = _backend_for(process_group, device)
+    state = native.BucketOptimizerState(backend, 1.0 / backend.size())
+    optimizer.attach_native_hook(state)
+    native._register_bucket_optimizer_hook(ddp.reducer, state)
+    ddp._mccl_native_hook_state = state
+    ddp.register_forward_pre_hook(lambda _m, _inp: optimizer.sync_native_hook())
 
 
 def wrap_ddp(module: torch.nn.Module, *, device_ids=None, bucket_cap_mb: Optional[int] = None,
@@ -135,8 +156,11 @@ def wrap_ddp(module: torch.nn.Module, *, device_ids=None, bucket_cap_mb: Optiona
     on_cuda = next(module.parameters()).is_cuda
     mode = compression if compression is not None else os.environ.get("MCCL_COMPRESSION", "none")
     if on_cuda and optimizer_in_backward is not None and mode != "topk":
-        ddp._mccl_oib_state = OptimizerInBackward(optimizer_in_backward, process_group)
-        ddp.register_comm_hook(ddp._mccl_oib_state, optimizer_in_backward_hook)
+        if os.environ.get("MCCL_PYTHON_BUCKET_HOOK", "0") == "1":
+            ddp._mccl_oib_state = OptimizerInBackward(optimizer_in_backward, process_group)
+            ddp.register_comm_hook(ddp._mccl_oib_state, optimizer_in_backward_hook)
+        else:
+            _install_native_bucket_hook(ddp, optimizer_in_backward, process_group)
     elif on_cuda and mode == "topk":
         ddp._mccl_topk_state = TopKState(process_group)
         ddp.register_comm_hook(ddp._mccl_topk_state, topk_hook)

@@ -69,6 +69,13 @@ try:
 except BaseException:
     traceback.print_exc()
     code = 1
+    # leave in order even after a failure: the group's shutdown drains the streams and releases
+    # device memory that peers can reach (all its waits are bounded)
+    try:
+        if {init_pg!r} and dist.is_initialized():
+            dist.destroy_process_group()
+    except BaseException:
+        pass
 sys.stdout.flush(); sys.stderr.flush()
 os._exit(code)
 """
@@ -105,6 +112,9 @@ def run_workers(
     child_env.setdefault("MCCL_LOG_LEVEL", "WARN")
     child_env.setdefault("MCCL_DEVICE_WAIT_US", "5000000")
     child_env.setdefault("OMP_NUM_THREADS", "1")
+    # NVLS (NVLink multicast) stays off in test workers unless a test asks for it: a rank that
+    # leaves abnormally while its memory is bound to a multicast object can fault its peers' GPUs.
+    child_env.setdefault("MCCL_NVLS", "0")
     if env:
         child_env.update({k: str(v) for k, v in env.items()})
     procs = []

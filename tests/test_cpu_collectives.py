@@ -219,3 +219,38 @@ def _pair_large(rank, ws):
 @pytest.mark.parametrize("env", [{}, {"MCCL_CHUNK_BYTES": "65536", "MCCL_TRANSPORT_CRC": "1"}], ids=["defaults", "small-frames-crc"])
 def test_two_rank_large_allreduce_segmented(env):
     run_workers(_pair_large, 2, timeout=240, env=env)
+
+
+def _nan_and_signed_zero(rank, ws):
+    import math
+    import torch, torch.distributed as dist
+    # Rank 0 and rank 1 reduce the same pair in opposite operand orders (each reduces its own buffer
+    # in place); MIN / MAX must still give the same bits on both: NaNs propagate, -0 orders below +0.
+    nan, inf = float("nan"), float("inf")
+    a = [nan, 1.0, 0.0, -0.0, 2.0, -inf, nan]
+    b = [1.0, nan, -0.0, 0.0, 2.0, 5.0, nan]
+    for op, want in ((dist.ReduceOp.MIN, [nan, nan, -0.0, -0.0, 2.0, -inf, nan]),
+                     (dist.ReduceOp.MAX, [nan, nan, 0.0, 0.0, 2.0, 5.0, nan])):
+        for dtype in (torch.float32, torch.float64, torch.bfloat16):
+            t = torch.tensor(a if rank == 0 else b, dtype=dtype)
+            dist.all_reduce(t, op=op)
+            outs = [torch.empty_like(t) for _ in range(ws)]
+            dist.all_gather(outs, t)
+            assert torch.equal(outs[0].view(torch.int16 if dtype == torch.bfloat16 else torch.int32 if dtype == torch.float32 else torch.int64),
+                               outs[1].view(torch.int16 if dtype == torch.bfloat16 else torch.int32 if dtype == torch.float32 else torch.int64)), (op, dtype)
+            for got, w in zip(t.double().tolist(), want):
+                if math.isnan(w):
+                    assert math.isnan(got), (op, dtype, got)
+                else:
+                    assert got == w and math.copysign(1.0, got) == math.copysign(1.0, w), (op, dtype, got, w)
+    # large enough for the segmented two-rank path
+    n = 3 * (1 << 20)
+    t = torch.zeros(n)
+    t[::2] = -0.0 if rank == 0 else 0.0
+    t[1::2] = nan if rank == 1 else 3.0
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    assert math.copysign(1.0, t[0].item()) == -1.0 and math.isnan(t[1].item()) and math.isnan(t[-1].item())
+
+
+def test_min_max_nan_and_signed_zero_agree_across_two_ranks():
+    run_workers(_nan_and_signed_zero, 2, timeout=120)

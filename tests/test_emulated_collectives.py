@@ -286,3 +286,145 @@ def test_reduce_scatter_reads_slices_in_place(native, cuda_device, ws):
     torch.cuda.synchronize()
     for r in range(ws):
         assert torch.allclose(outs[r].double(), want[r * n:(r + 1) * n], rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("ws", [2, 3, 8])
+@pytest.mark.parametrize("tile_bytes", [0, 8192, 65536])
+def test_allgather_tile_pipeline_and_slices(native, cuda_device, ws, tile_bytes):
+    # push + per-tile flags + copy-out; small tiles force many pipeline iterations per CTA.
+    # Also gathers a block in two slices that land at their final (strided) place.
+    g = native.EmuGroup(ws, 16 << 20)
+    for n in (1, 4099, 600_001):
+        ins = [((torch.arange(n, device=cuda_device) * 7 + r * 13) % 255).to(torch.uint8) for r in range(ws)]
+        want = torch.cat(ins)
+        outs = [torch.zeros(n * ws, dtype=torch.uint8, device=cuda_device) for _ in range(ws)]
+        g.allgather(outs, ins, 4, tile_bytes)
+        torch.cuda.synchronize()
+        for r in range(ws):
+            assert torch.equal(outs[r], want), (n, r)
+        if n > 1024:
+            cut = (n // 2) // 256 * 256
+            outs = [torch.zeros(n * ws, dtype=torch.uint8, device=cuda_device) for _ in range(ws)]
+            g.allgather(outs, ins, 4, tile_bytes, n, cut, 0)
+            g.allgather(outs, ins, 4, tile_bytes, n, n - cut, cut)
+            torch.cuda.synchronize()
+            for r in range(ws):
+                assert torch.equal(outs[r], want), ("sliced", n, r)
+
+
+@pytest.mark.parametrize("ws", [2, 5])
+def test_allgather_in_place(native, cuda_device, ws):
+    # torch's all_gather_into_tensor allows input == own slice of the output
+    g = native.EmuGroup(ws, 8 << 20)
+    n = 70001
+    outs = [torch.zeros(n * ws, device=cuda_device) for _ in range(ws)]
+    ins = []
+    for r in range(ws):
+        outs[r][r * n:(r + 1) * n] = torch.arange(n, device=cuda_device, dtype=torch.float32) + 1000 * r
+        ins.append(outs[r][r * n:(r + 1) * n])
+    want = torch.cat([i.clone() for i in ins])
+    g.allgather(outs, ins)
+    torch.cuda.synchronize()
+    for r in range(ws):
+        assert torch.equal(outs[r], want)
+
+
+@pytest.mark.parametrize("ws", [3, 4, 8])
+@pytest.mark.parametrize("tile_bytes", [8192, 0])
+def test_broadcast_two_hop_tiles_and_odd_sizes(native, cuda_device, ws, tile_bytes):
+    # above 256 KiB the root sends each slice to one owner, which forwards it; every size here has a
+    # ragged last slice, and small tiles make every CTA run several pipeline iterations
+    g = native.EmuGroup(ws, 16 << 20)
+    for nbytes in (262_145, 1_000_003, 4_194_304 + 16):
+        for root in (0, ws - 1, 1):
+            ts = [torch.full((nbytes,), r + 1, dtype=torch.uint8, device=cuda_device) for r in range(ws)]
+            ts[root] = ((torch.arange(nbytes, device=cuda_device) * 31 + root) % 251).to(torch.uint8)
+            want = ts[root].clone()
+            g.broadcast(ts, root, 4, tile_bytes)
+            torch.cuda.synchronize()
+            for r in range(ws):
+                assert torch.equal(ts[r], want), (nbytes, root, r)
+
+
+def test_broadcast_unaligned_views(native, cuda_device):
+    # tensors that start at odd byte offsets take the guarded (element-wise) load/store path
+    ws = 4
+    g = native.EmuGroup(ws, 8 << 20)
+    for n in (5, 70001, 400_003):
+        base = [torch.zeros(n + 3, dtype=torch.uint8, device=cuda_device) for _ in range(ws)]
+        ts = [b[1 + (r % 2):1 + (r % 2) + n] for r, b in enumerate(base)]
+        ts[2].copy_((torch.arange(n, device=cuda_device) % 199).to(torch.uint8))
+        want = ts[2].clone()
+        g.broadcast(ts, 2)
+        torch.cuda.synchronize()
+        for r in range(ws):
+            assert torch.equal(ts[r], want)
+            assert base[r][0].item() == 0 and base[r][-1].item() == 0  # nothing written outside the view
+
+
+def test_poisoned_buffers_between_epochs(native, cuda_device):
+    # All data buffers are filled with 0xFF (NaNs) before every collective: a kernel that consumed a
+    # slot nobody wrote in the current epoch would produce NaNs or wrong bytes.
+    ws = 4
+    g = native.EmuGroup(ws, 8 << 20)
+    for it in range(24):
+        g.poison_buffers(0xFF)
+        n = [17, 50_000, 4097, 300_000][it % 4]
+        xs = [torch.full((n,), float(it + r), device=cuda_device) for r in range(ws)]
+        g.allreduce(xs, "sum", "oneshot" if it % 3 else "twoshot", "none", 1.0, 0, 1, it % 2 == 1)
+        want = float(sum(it + r for r in range(ws)))
+        torch.cuda.synchronize()
+        for r in range(ws):
+            assert torch.all(xs[r] == want), (it, r)
+        g.poison_buffers(0xFF)
+        ins = [torch.full((n,), float(r + it), device=cuda_device) for r in range(ws)]
+        outs = [torch.empty(n * ws, device=cuda_device) for _ in range(ws)]
+        g.allgather(outs, ins)
+        g.poison_buffers(0xFF)
+        ts = [torch.full((n,), float(r), device=cuda_device) for r in range(ws)]
+        g.broadcast(ts, it % ws)
+        rs_in = [torch.full((n * ws,), float(r + 1), device=cuda_device) for r in range(ws)]
+        rs_out = [torch.empty(n, device=cuda_device) for _ in range(ws)]
+        g.poison_buffers(0xFF)
+        g.reduce_scatter(rs_out, rs_in, "sum")
+        torch.cuda.synchronize()
+        for r in range(ws):
+            assert torch.equal(outs[r], torch.cat(ins)) and torch.all(ts[r] == float(it % ws))
+            assert torch.all(rs_out[r] == float(sum(range(1, ws + 1))))
+
+
+def test_debug_checks_pass_on_the_small_case_matrix_and_catch_a_short_buffer(native, cuda_device):
+    # MCCL_DEBUG_CHECKS: kernels verify the ranges they are about to use.  The whole small-case
+    # matrix must run clean under it; a buffer that is claimed to be smaller than the payload needs
+    # is reported as ERR_BOUNDS (code 2) without any access outside it.
+    ws = 4
+    g = native.EmuGroup(ws, 4 << 20, 500_000)
+    g.set_debug_checks(True)
+    for n in (1, 33, 4097, 70001):
+        for algo in ("oneshot", "twoshot"):
+            xs = _inputs(ws, n, torch.float32, cuda_device, seed=n)
+            want = _reference(xs, "sum")
+            g.allreduce(xs, "sum", algo)
+            torch.cuda.synchronize()
+            assert torch.allclose(xs[0].double(), want, rtol=1e-5, atol=1e-5)
+        ins = _inputs(ws, n, torch.float32, cuda_device, seed=1)
+        outs = [torch.empty(n * ws, device=cuda_device) for _ in range(ws)]
+        g.allgather(outs, ins)
+        ts = [torch.full((n,), float(r), device=cuda_device) for r in range(ws)]
+        g.broadcast(ts, 1)
+        torch.cuda.synchronize()
+        assert torch.equal(outs[2], torch.cat(ins)) and torch.all(ts[3] == 1.0)
+    assert g.status(0)[0] == 0
+    g.set_claimed_capacity(1024)          # the kernels are told the buffer holds 1 KiB
+    ins = _inputs(ws, 4096, torch.float32, cuda_device, seed=2)
+    outs = [torch.full((4096 * ws,), -1.0, device=cuda_device) for _ in range(ws)]
+    g.allgather(outs, ins)
+    torch.cuda.synchronize()
+    st = g.status(0)
+    assert st[0] == 2 and st[2] == 10, st  # ERR_BOUNDS at the allgather's range check
+    assert torch.all(outs[0] == -1.0)      # nothing was written
+    g.clear_status()
+    g.set_claimed_capacity(0)
+    g.allgather(outs, ins)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], torch.cat(ins))

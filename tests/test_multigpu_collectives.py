@@ -184,23 +184,48 @@ def _oib_worker(rank, ws):
         torch.manual_seed(3)
         return torch.nn.Sequential(torch.nn.Linear(256, 1024), torch.nn.GELU(), torch.nn.Linear(1024, 1024),
                                    torch.nn.GELU(), torch.nn.Linear(1024, 16)).to(device)
+    def groups(m):
+        # two param groups with different hyper-parameters; buckets hold members of both
+        decay = [p for p in m.parameters() if p.ndim > 1]
+        rest = [p for p in m.parameters() if p.ndim <= 1]
+        return [{"params": decay, "weight_decay": 0.1}, {"params": rest, "weight_decay": 0.0, "lr": 3e-3}]
     a, b = make(), make()
-    opt_a = FusedAdamW(a.parameters(), lr=1e-3)
-    opt_b = FusedAdamW(b.parameters(), lr=1e-3)
+    opt_a = FusedAdamW(groups(a), lr=1e-3)
+    opt_b = FusedAdamW(groups(b), lr=1e-3)
+    sched_a = torch.optim.lr_scheduler.StepLR(opt_a, step_size=2, gamma=0.5)
+    sched_b = torch.optim.lr_scheduler.StepLR(opt_b, step_size=2, gamma=0.5)
     da = wrap_ddp(a, device_ids=[device.index], bucket_cap_mb=1)                                 # step after backward
     db = wrap_ddp(b, device_ids=[device.index], bucket_cap_mb=1, optimizer_in_backward=opt_b)    # step per bucket
     g = torch.Generator().manual_seed(rank)
     for _ in range(6):
         x = torch.randn(16, 256, generator=g).to(device); y = torch.randint(0, 16, (16,), generator=g).to(device)
-        for d, o in ((da, opt_a), (db, opt_b)):
-            o.zero_grad(); torch.nn.functional.cross_entropy(d(x), y).backward(); o.step()
+        for d, o, s in ((da, opt_a, sched_a), (db, opt_b, sched_b)):
+            o.zero_grad(); torch.nn.functional.cross_entropy(d(x), y).backward(); o.step(); s.step()
     for p, q in zip(a.parameters(), b.parameters()):
         assert torch.equal(p, q), (p - q).abs().max()
     assert int(opt_b.state[next(b.parameters())]["step"].item()) == 6
     sd = opt_b.state_dict()   # same layout as torch.optim.AdamW: loads into it
-    ref = torch.optim.AdamW(b.parameters(), lr=1e-3); ref.load_state_dict(sd)
+    ref = torch.optim.AdamW(groups(b), lr=1e-3); ref.load_state_dict(sd)
+    # and against torch's own AdamW with the same groups and schedule, on the same data
+    c = make()
+    opt_c = torch.optim.AdamW(groups(c), lr=1e-3)
+    sched_c = torch.optim.lr_scheduler.StepLR(opt_c, step_size=2, gamma=0.5)
+    dc = wrap_ddp(c, device_ids=[device.index], bucket_cap_mb=1)
+    g = torch.Generator().manual_seed(rank)
+    for _ in range(6):
+        x = torch.randn(16, 256, generator=g).to(device); y = torch.randint(0, 16, (16,), generator=g).to(device)
+        opt_c.zero_grad(); torch.nn.functional.cross_entropy(dc(x), y).backward(); opt_c.step(); sched_c.step()
+    for p, q in zip(b.parameters(), c.parameters()):
+        assert torch.allclose(p, q, rtol=1e-4, atol=2e-5), (p - q).abs().max()
 
 
-@pytest.mark.parametrize("ws", [2])
+@pytest.mark.parametrize("ws", _world_sizes())
 def test_optimizer_in_backward_matches_regular_step(ws):
+    if ws > _ngpu():
+        pytest.skip("not enough GPUs")
     run_workers(_oib_worker, ws, device="cuda", timeout=240)
+
+
+def test_optimizer_in_backward_python_hook_matches_too():
+    # the Python form of the bucket hook (MCCL_PYTHON_BUCKET_HOOK=1) stays available and equivalent
+    run_workers(_oib_worker, 2, device="cuda", timeout=240, env={"MCCL_PYTHON_BUCKET_HOOK": "1"})

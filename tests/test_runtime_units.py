@@ -73,3 +73,16 @@ def test_collective_concurrency_caps_lanes(native, monkeypatch):
     pg = native._create_process_group(dist.HashStore(), 0, 1, datetime.timedelta(seconds=10))
     assert "lanes=2" in pg.describe()
     pg.shutdown()
+
+
+def test_tile_plan_is_a_partition_owned_by_cta_index(native):
+    # Every unit belongs to exactly one tile, tile g to CTA g % nctas, and the plan depends only on
+    # (units, grid, tile size): writer and reader of a tile are the same CTA index on every rank.
+    for units in (1, 2047, 2048, 2049, 62_500, 1_000_000, 8_388_608):
+        for nctas in (1, 4, 62, 64):
+            for tile_bytes in (0, 8192, 1 << 20):
+                tu, nt = native._tile_plan(units, nctas, 512, tile_bytes)
+                assert tu % (512 * 4) == 0 and tu > 0
+                assert (nt - 1) * tu < units <= nt * tu
+                per_cta = -(-nt // nctas)
+                assert per_cta <= 1024, "12-bit tile counters"

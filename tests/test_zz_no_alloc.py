@@ -49,6 +49,15 @@ def test_noalloc_matches_regular_entry_point_twice(native, cuda_device):
         assert pairs_ref.shape == pairs.shape
         assert torch.equal(pairs, pairs_ref), f"call {call}: selected pairs differ"
         assert torch.equal(res, res_ref), f"call {call}: residuals differ"
+        # and directly against the host implementation of the same selection rule
+        host = native.TopKCompressor(ratio)
+        wire = host.compress(g.cpu(), 0)
+        import numpy as np
+        kk = int(np.frombuffer(wire[:4], dtype=np.uint32)[0])
+        rec = np.frombuffer(wire[4:4 + kk * 8], dtype=np.uint32).reshape(kk, 2)
+        got = pairs.cpu().numpy().view(np.uint32)
+        assert kk == k and np.array_equal(got, rec), f"call {call}: differs from the host compressor"
+        assert torch.equal(res.cpu(), host.residual(0)), f"call {call}: residual differs from the host compressor"
 
 
 def test_noalloc_rejects_bad_sizes(native, cuda_device):
