@@ -78,6 +78,8 @@ ProcessGroupMCCL::ProcessGroupMCCL(const c10::intrusive_ptr<c10d::Store>& store,
       tuner_.set_oneshot_max_bytes(ws, static_cast<size_t>(options_->oneshot_max_bytes));
   if (options_->nvls_min_bytes >= -1)
     for (int ws = 0; ws <= kern::kMaxWorld; ++ws) tuner_.set_nvls_min_bytes(ws, options_->nvls_min_bytes);
+  if (env_int("MCCL_OVERLAP_CTAS", -1) >= 0)  // grid cap of collectives that share the GPU with backward (DDP buckets)
+    for (int ws = 0; ws <= kern::kMaxWorld; ++ws) tuner_.set_ctas_overlap(ws, static_cast<int>(env_int("MCCL_OVERLAP_CTAS", 0)));
   if (options_->comm_ctas > kern::kMaxCtasPerLane) {
     MCCL_WARN("MCCL_COMM_CTAS=%lld exceeds the %d CTAs one lane may use (two lanes must stay co-resident): clamped",
               (long long)options_->comm_ctas, kern::kMaxCtasPerLane);

@@ -118,6 +118,8 @@ class ProcessGroupMCCL : public c10d::Backend {
   // stream and covered by the returned Work (used to chain a bucket's optimizer kernel natively).
   c10::intrusive_ptr<c10d::Work> allreduce_scaled_then(std::vector<at::Tensor>& tensors, float scale,
                                                         std::function<void(cudaStream_t)> epilogue);
+  // Collective: a pool of multicast-bound device memory for user tensors (see runtime/nvls_pool.h).
+  bool create_nvls_user_pool(int64_t bytes, c10::DeviceIndex dev);
   // Test hook: next CUDA collective is skipped on this rank (peers must time out).
   void test_skip_next_launch() { skip_next_launch_.store(true); }
   Tuner& tuner() { return tuner_; }
@@ -176,6 +178,7 @@ class ProcessGroupMCCL : public c10d::Backend {
   std::string poison_reason_;
   std::atomic<bool> shut_down_{false};
   std::atomic<bool> skip_next_launch_{false};
+  uint64_t pool_checks_ = 0;  // Store keys of the pool-offset agreement rounds (same sequence on every rank)
   // MCCL_DEVICE_TIMING: 0 = never, 1 = every CUDA collective, N = every Nth (default 8).  Timed ops carry
   // an event pair and feed the latency statistics; the others are only counted (timing events cost a few
   // microseconds per call, which matters for latency-bound collectives).

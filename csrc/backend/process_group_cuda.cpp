@@ -15,11 +15,14 @@
 #include <cuda_runtime_api.h>
 #include <nvtx3/nvToolsExt.h>
 
+#include <set>
+
 #include "backend/process_group.h"
 #include "backend/tensor_checks.h"
 #include "common/log.h"
 #include "kernels/topk_api.h"
 #include "runtime/nvls.h"
+#include "runtime/nvls_pool.h"
 
 namespace mccl {
 
@@ -35,6 +38,9 @@ struct ProcessGroupMCCL::CudaState {
   cudaStream_t poll_stream = nullptr;
   std::unique_ptr<SymmetricArena> arena;
   std::unique_ptr<NvlsRegion> nvls;  // multicast-bound buffers (nullptr: not supported / switched off)
+  bool user_pool = false;       // this group owns the device's multicast-bound tensor pool
+  std::set<size_t> pool_offsets_ok;  // tensor offsets in that pool already checked to agree on every rank
+  std::set<size_t> pool_offsets_bad; // offsets that differ between ranks: those tensors take the staged paths
   bool p2p = false;
   bool stamps_always = false;  // MCCL_PHASE_STAMPS=1: every collective stamps, not only the timed ones
   std::string why_not;
@@ -98,7 +104,7 @@ bool ProcessGroupMCCL::device_failed_quick() const {
 // for), and only then unmap and unbind.
 void ProcessGroupMCCL::release_nvls() {
   std::lock_guard<std::mutex> g(cuda_mu_);
-  if (!cuda_ || !cuda_->nvls) return;
+  if (!cuda_ || (!cuda_->nvls && !cuda_->user_pool)) return;
   c10::cuda::OptionalCUDAGuard guard(cuda_->dev);
   for (auto& l : cuda_->lanes) cudaStreamSynchronize(l.stream());
   cudaDeviceSynchronize();
@@ -108,8 +114,45 @@ void ProcessGroupMCCL::release_nvls() {
   } catch (const std::exception& e) {
     MCCL_WARN("rank %d: peers did not all reach the NVLS tear-down rendezvous (%s); releasing anyway", getRank(), e.what());
   }
-  cuda_->nvls->release();
-  cuda_->nvls.reset();
+  if (cuda_->user_pool) {
+    // tensors in the pool may outlive this group: only the multicast side ends here
+    NvlsUserPool::get(cuda_->dev).end_multicast();
+    cuda_->user_pool = false;
+  }
+  if (cuda_->nvls) {
+    cuda_->nvls->release();
+    cuda_->nvls.reset();
+  }
+}
+
+// Collective: creates the device's pool of multicast-bound memory for user tensors (gradient
+// buckets) on this group.  Returns false, on every rank alike, when NVLS is not available.
+bool ProcessGroupMCCL::create_nvls_user_pool(int64_t bytes, c10::DeviceIndex dev) {
+  if (getSize() < 2 || options_->nvls == "0" || options_->nvls == "off") return false;
+  ensure_cuda(dev);
+  std::lock_guard<std::mutex> g(cuda_mu_);
+  if (!cuda_->p2p) return false;
+  if (cuda_->user_pool) return true;
+  c10::cuda::CUDAGuard guard(dev);
+  const auto timeout = std::chrono::milliseconds(env_int("MCCL_CONNECT_TIMEOUT_MS", 30000));
+  std::string why;
+  if (NvlsUserPool::get(dev).active()) why = "another process group already owns this device's pool";
+  // agree first: one rank that cannot must keep all of them off the path
+  auto votes = rendezvous_->exchange("nvls_pool_vote", why.empty() ? "ok" : why, timeout);
+  for (auto& v : votes)
+    if (v != "ok") {
+      MCCL_WARN("rank %d: no multicast-bound tensor pool (%s)", getRank(), v.c_str());
+      return false;
+    }
+  auto region = NvlsRegion::create(
+      getRank(), getSize(), static_cast<size_t>(bytes), 1, "pool",
+      [this, timeout](const std::string& tag, const std::string& mine) { return rendezvous_->exchange(tag, mine, timeout); }, &why);
+  if (!region) {
+    MCCL_INFO("rank %d: no multicast-bound tensor pool (%s)", getRank(), why.c_str());
+    return false;
+  }
+  cuda_->user_pool = NvlsUserPool::get(dev).attach(std::move(region));
+  return cuda_->user_pool;
 }
 
 void ProcessGroupMCCL::ensure_cuda(c10::DeviceIndex dev) {
@@ -559,6 +602,49 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allreduce(at::Tensor& t, c
   cp.reducing = true;
   cp.bus_factor = 2.0 * (ws - 1) / ws;
 
+  // Tensor inside the multicast-bound pool (a DDP bucket built by wrap_ddp): reduce it in place, in
+  // the switch, with no staging and a grid sized for this rank's chunk only.
+  if (cuda_->user_pool && wire == dt && kern::nvls_allreduce_supported(dt, dt, to_kern_op(op)) &&
+      options_->algo != "oneshot" && options_->algo != "twoshot" && t.nbytes() % 16 == 0 &&
+      (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0 &&
+      t.nbytes() >= static_cast<size_t>(env_int("MCCL_NVLS_INPLACE_MIN_BYTES", 1 << 20))) {
+    NvlsUserPool& pool = NvlsUserPool::get(dev);
+    if (pool.active() && pool.contains(t.data_ptr(), t.nbytes())) {
+      const size_t off = pool.offset_of(t.data_ptr());
+      if (!cuda_->pool_offsets_ok.count(off) && !cuda_->pool_offsets_bad.count(off)) {
+        // first sight of this tensor: every rank must hold it at the same offset (same allocation
+        // order everywhere); checked once through the Store, then remembered
+        const auto timeout = std::chrono::milliseconds(env_int("MCCL_CONNECT_TIMEOUT_MS", 30000));
+        auto all = rendezvous_->exchange("nvls_pool_off/" + std::to_string(pool_checks_++),
+                                         std::to_string(off) + ":" + std::to_string(t.nbytes()), timeout);
+        bool same = true;
+        for (auto& v : all) same = same && v == all[0];
+        if (same) cuda_->pool_offsets_ok.insert(off);
+        else cuda_->pool_offsets_bad.insert(off);
+      }
+      if (cuda_->pool_offsets_ok.count(off)) {
+        kern::CollParams p = cp.params();
+        p.ctx[0].in = t.data_ptr();
+        p.ctx[0].out = t.data_ptr();
+        p.ctx[0].nvls_uc = pool.uc();
+        p.ctx[0].nvls_mc = pool.mc();
+        p.nvls_offset = off;
+        p.nvls_capacity = pool.size();
+        p.count = n;
+        p.op = to_kern_op(op);
+        p.scale = (op == c10d::ReduceOp::AVG ? 1.0f / ws : 1.0f) * prescale;
+        // each rank's SMs only move its own chunk (the switch does the fan-in and fan-out): a small grid
+        kern::LaunchCfg lc = cp.cfg(t.nbytes() / ws, overlapped);
+        lc.ctas = std::min<int>(lc.ctas, static_cast<int>(env_int("MCCL_NVLS_INPLACE_CTAS", 32)));
+        if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_allreduce_nvls_inplace(p, dt, lc, cp.stream.stream()));
+        cp.algo = "nvls-inplace";
+        const uint64_t sent = t.nbytes() + t.nbytes() / ws;
+        metrics_.record_transport_bytes(sent, sent);
+        return cp.finish();
+      }
+    }
+  }
+
   const int cls = wsz <= 2 ? 1 : 0;
   const bool nvls_ok = cuda_->nvls != nullptr && kern::nvls_allreduce_supported(dt, wire, to_kern_op(op)) &&
                        options_->algo != "oneshot" && options_->algo != "twoshot";
@@ -736,6 +822,9 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_reduce_scatter(at::Tensor&
   CudaPath cp(*this, c10d::OpType::REDUCE_SCATTER, "mccl:reduce_scatter", in_flat.nbytes(), {out}, dev);
   cp.keep(in_flat);
   cp.keep(out);
+  cp.algo = "push";
+  cp.reducing = true;
+  cp.bus_factor = static_cast<double>(ws - 1) / ws;
   const size_t cap = cuda_->arena->parity_bytes();
   // slot = one chunk slice; ws slots per parity buffer.  Chunks larger than a slot go in slices:
   // launch i reduces elements [off, off + cnt) of every chunk, reading them in place (chunk q
@@ -763,6 +852,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_barrier() {
   const auto dev = cuda_->dev;
   c10::cuda::CUDAGuard guard(dev);
   CudaPath cp(*this, c10d::OpType::BARRIER, "mccl:barrier", 0, {}, dev);
+  cp.algo = "flags";
   kern::CollParams p = cp.params();
   cp.wait_all_lanes();
   if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_barrier(p, kern::LaunchCfg{}, cp.stream.stream()));
@@ -791,57 +881,77 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::allreduce_topk(at::Tensor& grad
   const int ws = getSize();
   const int64_t n = grad.numel();
   MCCL_CHECK_TENSOR(n > 0 && n < (int64_t(1) << 31), "allreduce_topk: element count out of range");
-  int64_t k = std::max<int64_t>(1, static_cast<int64_t>(std::floor(static_cast<double>(n) * ratio)));
-  k = std::min(k, n);
   const bool bf16 = grad.scalar_type() == at::kBFloat16;
   c10::cuda::CUDAGuard guard(dev);
 
   if (ws > 1) ensure_cuda(dev);
   const bool p2p = ws > 1 && cuda_ && cuda_->p2p;
   MCCL_CHECK(ws == 1 || p2p, "allreduce_topk needs the NVLink peer data plane (" << data_plane() << ")");
-  const size_t pair_bytes = static_cast<size_t>(k) * 8;
-  if (p2p) MCCL_CHECK(kern::topk_pad(pair_bytes) <= cuda_->arena->parity_bytes(), "top-k payload exceeds the arena");
+  auto k_for = [ratio](int64_t cnt) {
+    int64_t k = std::max<int64_t>(1, static_cast<int64_t>(std::floor(static_cast<double>(cnt) * ratio)));
+    return std::min(k, cnt);
+  };
+  // One exchange stages ws lists of k pairs in every rank's arena buffer.  A bucket whose lists do not
+  // fit is cut into equal segments, each selected and exchanged on its own (top-k per segment).
+  int64_t seg = n;
+  if (p2p) {
+    const size_t cap = cuda_->arena->parity_bytes();
+    while (kern::topk_pad(static_cast<size_t>(k_for(seg)) * 8) * ws > cap) seg = (seg / 2 + 1023) / 1024 * 1024;
+    MCCL_CHECK(seg >= 1024, "top-k payload cannot be made to fit the arena");
+  }
 
-  // scratch: radix histograms + counters + this rank's (idx,val) list
   cudaStream_t stream;
-  c10::intrusive_ptr<c10d::Work> result;
   std::unique_ptr<CudaPath> cp;
   at::Tensor scratch, pairs;
   if (p2p) {
-    cp = std::make_unique<CudaPath>(*this, c10d::OpType::ALLREDUCE, "mccl:all_reduce_topk", pair_bytes * ws,
-                                    std::vector<at::Tensor>{grad}, dev, /*serial=*/true);
+    cp = std::make_unique<CudaPath>(*this, c10d::OpType::ALLREDUCE, "mccl:all_reduce_topk",
+                                    static_cast<uint64_t>(k_for(n)) * 8 * ws, std::vector<at::Tensor>{grad}, dev,
+                                    /*serial=*/true);
     stream = cp->stream.stream();  // serial collectives run on lane stream 0 (or the caller's stream)
     cp->keep(grad);
     cp->keep(residual);
+    cp->algo = "topk";
+    cp->bus_factor = static_cast<double>(ws - 1);
   } else {
     stream = c10::cuda::getCurrentCUDAStream(dev).stream();
   }
   {
+    // scratch: radix histograms + counters; pairs: this rank's (idx,val) list of the largest segment
     c10::cuda::CUDAStreamGuard sg(p2p ? cp->stream : c10::cuda::getCurrentCUDAStream(dev));
     scratch = at::empty({static_cast<int64_t>(kern::topk_scratch_bytes())}, grad.options().dtype(at::kByte));
-    pairs = at::empty({k * 2}, grad.options().dtype(at::kInt));
+    pairs = at::empty({k_for(std::min(seg, n)) * 2}, grad.options().dtype(at::kInt));
   }
-  kern::TopkArgs a;
-  a.grad = grad.data_ptr();
-  a.grad_is_bf16 = bf16;
-  a.residual = residual.data_ptr<float>();
-  a.n = n;
-  a.k = k;
-  a.scratch = scratch.data_ptr();
-  a.pairs = pairs.data_ptr();
-  a.scale = scale;
-  if (!(cp && cp->skip)) MCCL_LAUNCH_CHECK(kern::launch_topk_select(a, stream));
+  const size_t gsz = grad.element_size();
+  uint64_t sent = 0;
+  for (int64_t off = 0; off < n; off += seg) {
+    const int64_t cnt = std::min(seg, n - off);
+    const int64_t k = k_for(cnt);
+    kern::TopkArgs a;
+    a.grad = static_cast<char*>(grad.data_ptr()) + off * gsz;
+    a.grad_is_bf16 = bf16;
+    a.residual = residual.data_ptr<float>() + off;
+    a.n = cnt;
+    a.k = k;
+    a.scratch = scratch.data_ptr();
+    a.pairs = pairs.data_ptr();
+    a.scale = scale;
+    if (!(cp && cp->skip)) MCCL_LAUNCH_CHECK(kern::launch_topk_select(a, stream));
+    if (p2p) {
+      kern::CollParams p = cp->params();
+      p.ctx[0].in = pairs.data_ptr();
+      p.ctx[0].out = const_cast<void*>(a.grad);
+      p.count = k;
+      p.scale = scale;
+      if (!cp->skip) MCCL_LAUNCH_CHECK(kern::launch_topk_exchange_scatter(p, a, cp->cfg(static_cast<size_t>(k) * 8 * ws), stream));
+      sent += static_cast<uint64_t>(k) * 8 * (ws - 1);
+    } else {
+      MCCL_LAUNCH_CHECK(kern::launch_topk_local_scatter(a, stream));
+    }
+  }
   if (p2p) {
-    kern::CollParams p = cp->params();
-    p.ctx[0].in = pairs.data_ptr();
-    p.ctx[0].out = grad.data_ptr();
-    p.count = k;
-    p.scale = scale;
-    if (!cp->skip) MCCL_LAUNCH_CHECK(kern::launch_topk_exchange_scatter(p, a, cp->cfg(pair_bytes * ws), stream));
-    metrics_.record_transport_bytes(pair_bytes * (ws - 1), pair_bytes * (ws - 1));
+    metrics_.record_transport_bytes(sent, sent);
     return cp->finish();
   }
-  MCCL_LAUNCH_CHECK(kern::launch_topk_local_scatter(a, stream));
   return completed_work(c10d::OpType::ALLREDUCE, {grad}, nullptr);
 }
 

@@ -36,6 +36,7 @@
 #include "runtime/arena.h"
 #include "runtime/engine.h"
 #include "runtime/mempool.h"
+#include "runtime/nvls_pool.h"
 #include "runtime/watchdog.h"
 #ifdef MCCL_WITH_STFT
 #include "transforms/stft.h"
@@ -479,6 +480,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              });
            },
            py::arg("bucket"), py::arg("scale"), py::arg("specs"), py::arg("step"))
+      .def("create_nvls_user_pool",
+           [](ProcessGroupMCCL& pg, int64_t bytes, int device) { return pg.create_nvls_user_pool(bytes, static_cast<c10::DeviceIndex>(device)); },
+           py::arg("bytes"), py::arg("device"), py::call_guard<py::gil_scoped_release>(),
+           "Collective: binds a pool of device memory to an NVLink multicast object for zero-copy allreduce.")
       .def("_test_skip_next_launch", &ProcessGroupMCCL::test_skip_next_launch)
       .def("shutdown", &ProcessGroupMCCL::shutdown, py::call_guard<py::gil_scoped_release>());
 
@@ -648,6 +653,22 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       py::arg("reducer"), py::arg("state"),
       "Installs the native allreduce+AdamW bucket hook on a DistributedDataParallel reducer (ddp.reducer).");
 
+  // Drives the pool's range allocator with a script of (+bytes | -index) steps: +n allocates n bytes,
+  // -i releases the block returned by step i.  Returns (offsets, bytes in use, free blocks).
+  m.def("_test_range_allocator", [](int64_t size, std::vector<int64_t> steps) {
+    RangeAllocator ra;
+    ra.reset(static_cast<size_t>(size));
+    std::vector<int64_t> offs;
+    for (int64_t st : steps) {
+      if (st > 0) offs.push_back(ra.alloc(static_cast<size_t>(st)));
+      else offs.push_back(ra.release(static_cast<size_t>(offs.at(static_cast<size_t>(-st - 1)))) ? 0 : -2);
+    }
+    return std::make_tuple(offs, static_cast<int64_t>(ra.bytes_in_use()), static_cast<int64_t>(ra.free_blocks()));
+  });
+  m.def("_nvls_pool_bytes_in_use", [](int device) { return NvlsUserPool::get(device).bytes_in_use(); });
+  m.def("_nvls_pool_contains", [](const at::Tensor& t) {
+    return t.is_cuda() && NvlsUserPool::get(t.device().index()).contains(t.data_ptr(), t.nbytes());
+  });
   m.def("_kernel_launches", []() { return kern::launch_counter().load(); });
   // (tile_units, ntiles) the pipelined kernels derive for a 16-byte-unit index space and a grid
   m.def("_tile_plan", [](int64_t units, int nctas, int nthreads, int64_t tile_bytes) {

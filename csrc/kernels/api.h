@@ -133,6 +133,9 @@ cudaError_t launch_barrier(const CollParams& p, LaunchCfg cfg, cudaStream_t s);
 // (dtype, wire): F32/F32, F16/F16, BF16/BF16, F32/BF16, F32/F16; anything else returns
 // cudaErrorNotSupported before launching.
 bool nvls_allreduce_supported(DType dtype, DType wire, int op);
+// In place on a tensor that lives in multicast-bound memory: ctx[0].nvls_uc / nvls_mc are the bases of
+// that memory, nvls_offset the tensor's offset in it; count * sizeof(dtype) must be a multiple of 16.
+cudaError_t launch_allreduce_nvls_inplace(const CollParams& p, DType dtype, LaunchCfg cfg, cudaStream_t s);
 // `split`: the two local staging passes run as separate full-grid kernels around the kernel
 // that talks to the peers (large messages); otherwise one tile-pipelined kernel does all three.
 cudaError_t launch_allreduce_nvls(const CollParams& p, DType dtype, DType wire, LaunchCfg cfg, cudaStream_t s,

@@ -158,9 +158,10 @@ __device__ __forceinline__ bool range_ok(const CtaCtx& k, size_t off, size_t len
 // object; `multimem.ld_reduce` returns the element-wise sum over all ranks' copies, added up inside
 // the switch (16-bit floats are accumulated in fp32).  These are NVLS instructions on a multicast
 // *address*; they have nothing to do with TMA cluster multicast, which this library never uses.
+// The store is a weak one (ordered, like the plain peer stores, by the fence + release flag that
+// follows it); a strong sys-scope store per 16 bytes measured markedly slower.
 __device__ __forceinline__ void multimem_st16(void* mc, uint4 v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z),
-               "r"(v.w)
+  asm volatile("multimem.st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");
 }
 template <typename W> struct MultimemSum;

@@ -14,7 +14,7 @@
 
 namespace {
 
-constexpr size_t kScratchBytes = 48 * 1024;  // >= mccl::kern::topk_scratch_bytes(), checked at set-up
+constexpr size_t kScratchBytes = 64 * 1024;  // >= mccl::kern::topk_scratch_bytes(), checked at set-up
 constexpr int kMaxDevices = 64;
 
 static __device__ __align__(256) unsigned char g_noalloc_topk_scratch[kScratchBytes];

@@ -12,7 +12,7 @@
 // (adjusted = grad + residual; pick the k entries of largest magnitude, ties to
 // the lower index; write them as (u32 index, f32 value) pairs sorted by index;
 // residual = adjusted with the picked entries zeroed), but the kernels' scratch
-// (radix histograms, selection state, per-block counters: about 41 KB) lives in
+// (radix histograms, selection state, per-block counters: about 53 KB of a 64 KB array) lives in
 // one fixed device array that is part of the library image instead of being
 // allocated per call.
 //

@@ -305,6 +305,65 @@ __global__ void __launch_bounds__(512) nvls_reduce_bcast_kernel(const __grid_con
   stamp(k, 6);
 }
 
+// ---------------------------------------------------------------------------
+// In-place form for tensors that already live in multicast-bound memory (runtime/nvls_pool.h):
+// no staging at all.  Barrier (every rank's tensor is ready), the owner of a chunk reduces it in
+// the switch, scales it and multimem.st's the result over every rank's copy (its own included),
+// barrier (everybody's chunks have landed).  Each GPU's SMs touch only N/ws bytes, the links carry
+// (1 + 1/ws) N per direction, and the reduction costs no SM time: a gradient bucket is reduced by
+// a grid of a few CTAs while backward keeps the rest of the GPU.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(512) nvls_inplace_kernel(const __grid_constant__ CollParams p) {
+  using U = Unit<T, T>;
+  using Acc = typename U::Acc;
+  CtaCtx k = make_ctx(p);
+  const RankCtx& c = *k.c;
+  stamp(k, 0);
+  if (!enter_collective(k)) return;
+  stamp(k, 1);
+  const int64_t units = p.count / U::N;  // the launcher guarantees whole 16-byte units
+  const int64_t chunk_units = (units + c.ws - 1) / c.ws;
+  if (!range_ok(k, p.nvls_offset, static_cast<size_t>(units) * 16, p.nvls_capacity, 32)) return;
+  char* mc = c.nvls_mc + p.nvls_offset;
+  const bool scaled = p.op == AVG || p.scale != 1.0f;
+  stamp(k, 2);
+  signal_all(k, 0);
+  if (!wait_all(k, 0)) return;
+  stamp(k, 3);
+  const int64_t own0 = static_cast<int64_t>(c.rank) * chunk_units;
+  const int64_t own1 = own0 + chunk_units < units ? own0 + chunk_units : units;
+  constexpr int kIn = 8;
+  const int64_t stride = static_cast<int64_t>(k.nctas) * k.nthreads;
+  for (int64_t ub = own0 + static_cast<int64_t>(k.cta) * k.nthreads + k.tid; ub < own1; ub += stride * kIn) {
+    uint4 v[kIn];
+#pragma unroll
+    for (int i = 0; i < kIn; ++i) {
+      const int64_t u = ub + i * stride;
+      if (u < own1) v[i] = MultimemSum<T>::ld(mc + u * 16);
+    }
+#pragma unroll
+    for (int i = 0; i < kIn; ++i) {
+      const int64_t u = ub + i * stride;
+      if (u < own1) {
+        if (scaled) {
+          Acc a[U::N];
+          U::unpack_W(v[i], a);
+#pragma unroll
+          for (int j = 0; j < U::N; ++j) a[j] = Traits<T>::scale(a[j], p.scale);
+          v[i] = U::pack_W(a);
+        }
+        multimem_st16(mc + u * 16, v[i]);
+      }
+    }
+  }
+  stamp(k, 4);
+  signal_all(k, 1);
+  if (!wait_all(k, 1)) return;
+  stamp(k, 5);
+  stamp(k, 6);
+}
+
 template <typename T, typename W>
 cudaError_t go_split(const CollParams& p, int ctas, const LaunchCfg& cfg, cudaStream_t s) {
   const int64_t units = (p.count + Unit<T, W>::N - 1) / Unit<T, W>::N;
@@ -338,6 +397,18 @@ bool nvls_allreduce_supported(DType dtype, DType wire, int op) {
   if (dtype == F32) return wire == F32 || wire == BF16 || wire == F16;
   if (dtype == F16 || dtype == BF16) return wire == dtype;
   return false;
+}
+
+cudaError_t launch_allreduce_nvls_inplace(const CollParams& p, DType dtype, LaunchCfg cfg, cudaStream_t s) {
+  if (!nvls_allreduce_supported(dtype, dtype, p.op) || cfg.emulate_ranks > 0 || p.ctx[0].nvls_mc == nullptr)
+    return cudaErrorNotSupported;
+  if ((p.count * dtype_size(dtype)) % 16 != 0 || (p.nvls_offset % 16) != 0) return cudaErrorInvalidValue;
+  // each rank only moves its own chunk: size the grid for count / ws
+  const size_t own_bytes = p.count * dtype_size(dtype) / p.ctx[0].ws;
+  const int ctas = clamp_ctas(cfg.ctas > 0 ? cfg.ctas : pick_ctas(own_bytes, p.ctx[0].ws, 0), cfg);
+  if (dtype == F32) return do_launch(nvls_inplace_kernel<float>, p, ctas, cfg.threads, 0, s);
+  if (dtype == F16) return do_launch(nvls_inplace_kernel<__half>, p, ctas, cfg.threads, 0, s);
+  return do_launch(nvls_inplace_kernel<__nv_bfloat16>, p, ctas, cfg.threads, 0, s);
 }
 
 cudaError_t launch_allreduce_nvls(const CollParams& p, DType dtype, DType wire, LaunchCfg cfg, cudaStream_t s,

@@ -1,4 +1,5 @@
-// STFT / iSTFT kernels (sm_100a): block-per-frame shared-memory radix-2 FFT with
+// STFT / iSTFT kernels (sm_100a): shared-memory radix-2 FFTs of half the frame length (real
+// input / real output), several frames per CTA, twiddles computed once per CTA, with
 // the padding, windowing and scaling fused into the loads and stores, and an
 // atomics-free gather overlap-add.  See stft_api.h for the decomposition.
 // Replaces the reference's one-thread-per-frame Metal FFT (reference
@@ -15,27 +16,6 @@ namespace kern {
 namespace {
 
 __device__ __forceinline__ int bit_reverse(int x, int bits) { return __brev(static_cast<unsigned>(x)) >> (32 - bits); }
-
-// In-place radix-2 FFT over `data` (n complex values, already in bit-reversed
-// order).  `tw[k] = exp(-2*pi*i*k/n)`, k < n/2.  sign = -1 forward, +1 inverse.
-__device__ __forceinline__ void fft_smem(float2* data, const float2* tw, int n, int log2n, float sign) {
-  for (int s = 1; s <= log2n; ++s) {
-    const int half = 1 << (s - 1);
-    const int tstep = n >> s;
-    for (int j = threadIdx.x; j < n / 2; j += blockDim.x) {
-      const int pos = j & (half - 1);
-      const int i0 = ((j >> (s - 1)) << s) + pos;
-      const int i1 = i0 + half;
-      float2 w = tw[pos * tstep];
-      w.y *= -sign;  // table holds the forward twiddle (negative angle)
-      const float2 a = data[i0], b = data[i1];
-      const float2 t = make_float2(b.x * w.x - b.y * w.y, b.x * w.y + b.y * w.x);
-      data[i0] = make_float2(a.x + t.x, a.y + t.y);
-      data[i1] = make_float2(a.x - t.x, a.y - t.y);
-    }
-    __syncthreads();
-  }
-}
 
 __device__ __forceinline__ void fill_twiddles(float2* tw, int n) {
   for (int k = threadIdx.x; k < n / 2; k += blockDim.x) {
@@ -71,65 +51,144 @@ __device__ __forceinline__ float envelope_at(const float* window, int64_t p, int
   return e;
 }
 
-__global__ void __launch_bounds__(512) fft_frames_kernel(const FftFramesArgs a, int log2n) {
-  extern __shared__ float2 smem[];
-  float2* data = smem;
-  float2* tw = smem + a.n_fft;
-  const int frame = blockIdx.x, b = blockIdx.y;
-  const int n = a.n_fft;
-  fill_twiddles(tw, n);
-  const float* sig = a.signal + static_cast<int64_t>(b) * a.signal_len;
-  const int64_t start = static_cast<int64_t>(frame) * a.hop - a.pad;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    int64_t t = start + i;
-    float v = 0.f;
-    if (a.reflect) {
-      v = sig[reflect_index(t, a.signal_len)];
-    } else if (t >= 0 && t < a.signal_len) {
-      v = sig[t];
-      if (a.divide_envelope) {
-        const float e = envelope_at(a.window, t + a.pad, n, a.hop, a.n_frames);
-        v = e > 1e-11f ? v / e : 0.f;
-      }
+// Both transforms work on REAL frames, so each frame is handled as a complex FFT of half the
+// length: z[m] = x[2m] + i x[2m+1], Z = FFT_{N/2}(z), and one pass with the twiddles W_N^k
+// separates / recombines the even and odd halves.  That halves the butterflies and the shared
+// memory per frame.  A CTA computes the twiddle table once and then loops over frames, `fpc`
+// frames at a time (several short frames keep all threads busy).
+//
+//   forward:  E[k] = (Z[k] + conj Z[h-k]) / 2,  O[k] = (Z[k] - conj Z[h-k]) / (2i),
+//             X[k] = E[k] + W_N^k O[k],  k = 0..h  (h = N/2, Z[h] = Z[0])
+//   inverse:  Z[k] = (X[k] + conj X[h-k]) + i W_N^{-k} (X[k] - conj X[h-k]),  z = IFFT_h(Z) (no 1/h),
+//             y[2m] = Re z[m], y[2m+1] = Im z[m]   (y = unnormalised inverse of the Hermitian extension)
+
+// Radix-2 passes over `fpc` independent transforms of length h stored back to back in `data`
+// (bit-reversed order on entry).  tw[k] = exp(-2*pi*i*k/N) with N = 2h, so W_h^k = tw[2k].
+__device__ __forceinline__ void fft_half_smem(float2* data, const float2* tw, int h, int log2h, int fpc, float sign) {
+  const int per = h / 2;
+  for (int s = 1; s <= log2h; ++s) {
+    const int half = 1 << (s - 1);
+    const int tstep = (h >> s) * 2;
+    for (int jj = threadIdx.x; jj < per * fpc; jj += blockDim.x) {
+      const int f = jj / per, j = jj - f * per;
+      float2* d = data + f * h;
+      const int pos = j & (half - 1);
+      const int i0 = ((j >> (s - 1)) << s) + pos;
+      const int i1 = i0 + half;
+      float2 w = tw[pos * tstep];
+      w.y *= -sign;  // table holds the forward twiddle (negative angle)
+      const float2 a = d[i0], b = d[i1];
+      const float2 t = make_float2(b.x * w.x - b.y * w.y, b.x * w.y + b.y * w.x);
+      d[i0] = make_float2(a.x + t.x, a.y + t.y);
+      d[i1] = make_float2(a.x - t.x, a.y - t.y);
     }
-    data[bit_reverse(i, log2n)] = make_float2(v * a.window[i], 0.f);
-  }
-  __syncthreads();
-  fft_smem(data, tw, n, log2n, -1.0f);
-  const int bins = n / 2 + 1;
-  float2* out = reinterpret_cast<float2*>(a.out) + (static_cast<int64_t>(b) * a.n_frames + frame) * bins;
-  for (int k = threadIdx.x; k < bins; k += blockDim.x) {
-    float s = a.scale;
-    if (a.hermitian_weights && k != 0 && k != n / 2) s *= 2.0f;
-    float2 v = data[k];
-    if (a.hermitian_weights && (k == 0 || k == n / 2)) v.y = 0.f;  // imaginary parts of DC/Nyquist are ignored by an inverse real FFT
-    out[k] = make_float2(v.x * s, v.y * s);
+    __syncthreads();
   }
 }
 
-__global__ void __launch_bounds__(512) ifft_frames_kernel(const IfftFramesArgs a, int log2n) {
-  extern __shared__ float2 smem[];
-  float2* data = smem;
-  float2* tw = smem + a.n_fft;
-  const int frame = blockIdx.x, b = blockIdx.y;
-  const int n = a.n_fft;
-  fill_twiddles(tw, n);
-  const float2* spec = reinterpret_cast<const float2*>(a.spec) + b * a.stride_b + frame * a.stride_t;
-  for (int k = threadIdx.x; k < n; k += blockDim.x) {
-    float2 v = make_float2(0.f, 0.f);
-    if (k <= n / 2) {
-      v = spec[k * a.stride_f];
-      if (a.hermitian && (k == 0 || k == n / 2)) v.y = 0.f;
-    } else if (a.hermitian) {
-      const float2 m = spec[(n - k) * a.stride_f];
-      v = make_float2(m.x, -m.y);
+__device__ __forceinline__ float load_sample(const FftFramesArgs& a, const float* sig, int64_t t, int n) {
+  float v = 0.f;
+  if (a.reflect) {
+    v = sig[reflect_index(t, a.signal_len)];
+  } else if (t >= 0 && t < a.signal_len) {
+    v = sig[t];
+    if (a.divide_envelope) {
+      const float e = envelope_at(a.window, t + a.pad, n, a.hop, a.n_frames);
+      v = e > 1e-11f ? v / e : 0.f;
     }
-    data[bit_reverse(k, log2n)] = v;
   }
-  __syncthreads();
-  fft_smem(data, tw, n, log2n, +1.0f);
-  float* out = a.frames + (static_cast<int64_t>(b) * a.n_frames + frame) * n;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) out[i] = data[i].x * a.scale * a.window[i];
+  return v;
+}
+
+__global__ void __launch_bounds__(256) fft_frames_kernel(const FftFramesArgs a, int log2h, int fpc) {
+  extern __shared__ float2 smem[];
+  const int n = a.n_fft, h = n / 2;
+  float2* tw = smem;        // h twiddles W_N^k
+  float2* data = smem + h;  // fpc * h values
+  const int b = blockIdx.y;
+  fill_twiddles(tw, n);
+  const float* sig = a.signal + static_cast<int64_t>(b) * a.signal_len;
+  const int bins = h + 1;
+  for (int f0 = blockIdx.x * fpc; f0 < a.n_frames; f0 += gridDim.x * fpc) {
+    __syncthreads();  // twiddles ready / previous frames' bins written
+    for (int jj = threadIdx.x; jj < h * fpc; jj += blockDim.x) {
+      const int f = jj / h, m = jj - f * h;
+      const int frame = f0 + f;
+      float v0 = 0.f, v1 = 0.f;
+      if (frame < a.n_frames) {
+        const int64_t start = static_cast<int64_t>(frame) * a.hop - a.pad;
+        v0 = load_sample(a, sig, start + 2 * m, n) * a.window[2 * m];
+        v1 = load_sample(a, sig, start + 2 * m + 1, n) * a.window[2 * m + 1];
+      }
+      data[f * h + bit_reverse(m, log2h)] = make_float2(v0, v1);
+    }
+    __syncthreads();
+    fft_half_smem(data, tw, h, log2h, fpc, -1.0f);
+    for (int jj = threadIdx.x; jj < bins * fpc; jj += blockDim.x) {
+      const int f = jj / bins, k = jj - f * bins;
+      const int frame = f0 + f;
+      if (frame >= a.n_frames) continue;
+      const float2* d = data + f * h;
+      const float2 zk = d[k == h ? 0 : k];
+      const float2 zm = d[(h - k) & (h - 1)];            // Z[h-k], with Z[h] = Z[0]
+      const float2 e = make_float2(0.5f * (zk.x + zm.x), 0.5f * (zk.y - zm.y));
+      const float2 o = make_float2(0.5f * (zk.y + zm.y), -0.5f * (zk.x - zm.x));   // (Zk - conj Zm) / (2i)
+      const float2 w = k == h ? make_float2(-1.f, 0.f) : tw[k];
+      float2 v = make_float2(e.x + w.x * o.x - w.y * o.y, e.y + w.x * o.y + w.y * o.x);
+      float sc = a.scale;
+      if (a.hermitian_weights && k != 0 && k != h) sc *= 2.0f;
+      if (a.hermitian_weights && (k == 0 || k == h)) v.y = 0.f;  // imaginary parts of DC/Nyquist are ignored by an inverse real FFT
+      float2* out = reinterpret_cast<float2*>(a.out) + (static_cast<int64_t>(b) * a.n_frames + frame) * bins;
+      out[k] = make_float2(v.x * sc, v.y * sc);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) ifft_frames_kernel(const IfftFramesArgs a, int log2h, int fpc) {
+  extern __shared__ float2 smem[];
+  const int n = a.n_fft, h = n / 2;
+  float2* tw = smem;
+  float2* data = smem + h;
+  const int b = blockIdx.y;
+  fill_twiddles(tw, n);
+  // hermitian: inverse real FFT of the one-sided bins.  Otherwise the adjoint of the forward
+  // transform, Re(sum_{k<=h} X[k] e^{+2 pi i k n / N}), which equals half the inverse real FFT of the
+  // same bins with the real parts of DC and Nyquist doubled.
+  const float edge = a.hermitian ? 1.0f : 2.0f;
+  const float post = a.hermitian ? a.scale : 0.5f * a.scale;
+  for (int f0 = blockIdx.x * fpc; f0 < a.n_frames; f0 += gridDim.x * fpc) {
+    __syncthreads();
+    for (int jj = threadIdx.x; jj < h * fpc; jj += blockDim.x) {
+      const int f = jj / h, k = jj - f * h;
+      const int frame = f0 + f;
+      float2 z = make_float2(0.f, 0.f);
+      if (frame < a.n_frames) {
+        const float2* spec = reinterpret_cast<const float2*>(a.spec) + b * a.stride_b + frame * a.stride_t;
+        float2 xk = spec[k * a.stride_f];
+        float2 xm = spec[(h - k) * a.stride_f];
+        if (k == 0) {  // pair (DC, Nyquist): imaginary parts do not take part
+          xk = make_float2(edge * xk.x, 0.f);
+          xm = make_float2(edge * xm.x, 0.f);
+        }
+        const float2 ep = make_float2(xk.x + xm.x, xk.y - xm.y);   // X[k] + conj X[h-k]
+        const float2 dm = make_float2(xk.x - xm.x, xk.y + xm.y);   // X[k] - conj X[h-k]
+        const float2 w = make_float2(tw[k].x, -tw[k].y);           // W_N^{-k}
+        const float2 od = make_float2(dm.x * w.x - dm.y * w.y, dm.x * w.y + dm.y * w.x);
+        z = make_float2(ep.x - od.y, ep.y + od.x);                 // E' + i O'
+      }
+      data[f * h + bit_reverse(k, log2h)] = z;
+    }
+    __syncthreads();
+    fft_half_smem(data, tw, h, log2h, fpc, +1.0f);
+    for (int jj = threadIdx.x; jj < h * fpc; jj += blockDim.x) {
+      const int f = jj / h, m = jj - f * h;
+      const int frame = f0 + f;
+      if (frame >= a.n_frames) continue;
+      const float2 v = data[f * h + m];
+      float2* out = reinterpret_cast<float2*>(a.frames + (static_cast<int64_t>(b) * a.n_frames + frame) * n);
+      out[m] = make_float2(v.x * post * a.window[2 * m], v.y * post * a.window[2 * m + 1]);
+    }
+  }
 }
 
 __device__ __forceinline__ float ola_at(const float* frames, int64_t p, int n_fft, int hop, int n_frames) {
@@ -175,23 +234,40 @@ int ilog2(int n) {
 
 bool valid_nfft(int n) { return n >= 8 && n <= kStftMaxNfft && (n & (n - 1)) == 0; }
 
+// Frames handled together by one CTA iteration and the grid: enough frames per iteration to give
+// every thread butterflies, enough CTAs to fill the GPU a few times over, each looping over frames.
+void frame_grid(int n_fft, int n_frames, int batch, int* fpc, int* grid_x, size_t* smem) {
+  const int h = n_fft / 2;
+  int f = 512 / h;  // 256 threads, h/2 butterflies per frame and stage
+  if (f < 1) f = 1;
+  if (f > 8) f = 8;
+  *fpc = f;
+  int64_t want = (static_cast<int64_t>(n_frames) + f - 1) / f;
+  int64_t cap = (148 * 8 + batch - 1) / batch;
+  if (cap < 1) cap = 1;
+  *grid_x = static_cast<int>(want < cap ? want : cap);
+  *smem = (static_cast<size_t>(h) + static_cast<size_t>(f) * h) * sizeof(float2);
+}
+
 }  // namespace
 
 cudaError_t launch_fft_frames(const FftFramesArgs& a, cudaStream_t s) {
   if (!valid_nfft(a.n_fft) || a.batch <= 0 || a.n_frames <= 0) return cudaErrorInvalidValue;
   note_launch();
-  const int threads = a.n_fft / 2 < 512 ? (a.n_fft / 2 < 32 ? 32 : a.n_fft / 2) : 512;
-  const size_t smem = static_cast<size_t>(a.n_fft) * 8 + static_cast<size_t>(a.n_fft) * 4;
-  fft_frames_kernel<<<dim3(a.n_frames, a.batch), threads, smem, s>>>(a, ilog2(a.n_fft));
+  int fpc, gx;
+  size_t smem;
+  frame_grid(a.n_fft, a.n_frames, a.batch, &fpc, &gx, &smem);
+  fft_frames_kernel<<<dim3(gx, a.batch), 256, smem, s>>>(a, ilog2(a.n_fft / 2), fpc);
   return cudaGetLastError();
 }
 
 cudaError_t launch_ifft_frames(const IfftFramesArgs& a, cudaStream_t s) {
   if (!valid_nfft(a.n_fft) || a.batch <= 0 || a.n_frames <= 0) return cudaErrorInvalidValue;
   note_launch();
-  const int threads = a.n_fft / 2 < 512 ? (a.n_fft / 2 < 32 ? 32 : a.n_fft / 2) : 512;
-  const size_t smem = static_cast<size_t>(a.n_fft) * 8 + static_cast<size_t>(a.n_fft) * 4;
-  ifft_frames_kernel<<<dim3(a.n_frames, a.batch), threads, smem, s>>>(a, ilog2(a.n_fft));
+  int fpc, gx;
+  size_t smem;
+  frame_grid(a.n_fft, a.n_frames, a.batch, &fpc, &gx, &smem);
+  ifft_frames_kernel<<<dim3(gx, a.batch), 256, smem, s>>>(a, ilog2(a.n_fft / 2), fpc);
   return cudaGetLastError();
 }
 

@@ -25,11 +25,15 @@ struct TopkState {
   uint32_t need;      // how many more elements must come from the current bin
   uint32_t threshold; // final: 31-bit magnitude key of the k-th element
   uint32_t need_eq;   // final: number of ties (key == threshold) to take
-  uint32_t nblocks;
-  uint32_t pad[3];
+  uint32_t ncand;     // candidates appended by the collect pass (may exceed the capacity)
+  uint32_t overflow;  // 1: the candidate list did not fit -> the full-vector refinement runs
+  uint32_t ticket[5]; // "last block done" counters: adjust, collect, level 1, level 2, count
+  uint32_t pad[1];
 };
 struct TopkScratch {
-  uint32_t hist[3][kTopkBins];
+  uint32_t hist0[kTopkBins0];
+  uint32_t hist1[kTopkBins12];
+  uint32_t hist2[kTopkBins12];
   TopkState st;
   uint32_t blk_gt[kTopkMaxBlocks];
   uint32_t blk_eq[kTopkMaxBlocks];
@@ -39,63 +43,24 @@ struct TopkScratch {
 
 __device__ __forceinline__ uint32_t mag_key(float a) { return __float_as_uint(a) & 0x7FFFFFFFu; }
 
-// level 0: bits 30..20 (11), level 1: bits 19..9 (11), level 2: bits 8..0 (9)
+// level 0: bits 30..18 (13), level 1: bits 17..9 (9), level 2: bits 8..0 (9)
 __device__ __forceinline__ uint32_t digit_of(uint32_t key, int level) {
-  return level == 0 ? (key >> 20) : level == 1 ? ((key >> 9) & 0x7FFu) : (key & 0x1FFu);
+  return level == 0 ? (key >> 18) : level == 1 ? ((key >> 9) & 0x1FFu) : (key & 0x1FFu);
 }
 __device__ __forceinline__ bool prefix_matches(uint32_t key, int level, uint32_t prefix) {
-  return level == 0 ? true : level == 1 ? ((key >> 20) == prefix) : ((key >> 9) == prefix);
+  return level == 0 ? true : level == 1 ? ((key >> 18) == prefix) : ((key >> 9) == prefix);
+}
+__device__ __forceinline__ uint32_t* hist_of(TopkScratch* sc, int level) {
+  return level == 0 ? sc->hist0 : level == 1 ? sc->hist1 : sc->hist2;
 }
 
 __global__ void topk_clear_kernel(TopkScratch* sc) {
-  uint32_t* h = &sc->hist[0][0];
-  for (int i = threadIdx.x + blockIdx.x * blockDim.x; i < 3 * kTopkBins; i += blockDim.x * gridDim.x) h[i] = 0;
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    sc->st.prefix = 0;
-    sc->st.need = 0;
-    sc->st.threshold = 0;
-    sc->st.need_eq = 0;
-  }
+  uint32_t* h = sc->hist0;  // hist0, hist1, hist2 are contiguous
+  for (int i = threadIdx.x + blockIdx.x * blockDim.x; i < kTopkBins0 + 2 * kTopkBins12; i += blockDim.x * gridDim.x) h[i] = 0;
+  if (blockIdx.x == 0 && threadIdx.x < sizeof(TopkState) / 4) reinterpret_cast<uint32_t*>(&sc->st)[threadIdx.x] = 0;
 }
 
-// a = g + e, e = a, histogram of the top digit.
-template <bool kBf16>
-__global__ void __launch_bounds__(512) topk_adjust_hist_kernel(const void* __restrict__ grad,
-                                                               float* __restrict__ res, int64_t n,
-                                                               TopkScratch* sc) {
-  __shared__ uint32_t sh[kTopkBins];
-  for (int i = threadIdx.x; i < kTopkBins; i += blockDim.x) sh[i] = 0;
-  __syncthreads();
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
-    float g = kBf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(grad)[i])
-                    : static_cast<const float*>(grad)[i];
-    float a = g + res[i];
-    res[i] = a;
-    atomicAdd(&sh[digit_of(mag_key(a), 0)], 1u);
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i < kTopkBins; i += blockDim.x)
-    if (sh[i]) atomicAdd(&sc->hist[0][i], sh[i]);
-}
-
-__global__ void __launch_bounds__(512) topk_hist_level_kernel(const float* __restrict__ res, int64_t n,
-                                                              TopkScratch* sc, int level) {
-  __shared__ uint32_t sh[kTopkBins];
-  for (int i = threadIdx.x; i < kTopkBins; i += blockDim.x) sh[i] = 0;
-  __syncthreads();
-  const uint32_t prefix = sc->st.prefix;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
-    uint32_t key = mag_key(res[i]);
-    if (prefix_matches(key, level, prefix)) atomicAdd(&sh[digit_of(key, level)], 1u);
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i < kTopkBins; i += blockDim.x)
-    if (sh[i]) atomicAdd(&sc->hist[level][i], sh[i]);
-}
-
-// Exclusive scan of one value per thread over a 1024-thread block.
+// Exclusive scan of one value per thread over a block of up to 1024 threads.
 __device__ __forceinline__ uint32_t block_excl_scan(uint32_t v, uint32_t* warp_sums, uint32_t& total) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   uint32_t inc = v;
@@ -122,10 +87,10 @@ __device__ __forceinline__ uint32_t block_excl_scan(uint32_t v, uint32_t* warp_s
   return excl;
 }
 
-// Walks the histogram of `level` from the top bin down (as a parallel suffix
-// scan: thread t owns bins 2047-2t and 2046-2t) and fixes the next digit: the
-// first bin, from the top, at which the running count reaches `need`.
-__global__ void __launch_bounds__(1024) topk_pick_bin_kernel(TopkScratch* sc, int level, uint32_t k) {
+// Walks a histogram from the top bin down (as a parallel suffix scan: every thread owns a run of
+// consecutive bins) and fixes the next digit: the first bin, from the top, at which the running
+// count reaches `need`.  Called by every thread of one block; `hist` may be global or shared.
+__device__ void pick_bin_block(TopkScratch* sc, const uint32_t* hist, int nbins, int level, uint32_t k) {
   __shared__ uint32_t wsum[33];
   __shared__ uint32_t s_digit, s_cum;
   const uint32_t need = level == 0 ? k : sc->st.need;
@@ -134,47 +99,277 @@ __global__ void __launch_bounds__(1024) topk_pick_bin_kernel(TopkScratch* sc, in
     s_digit = 0;
     s_cum = 0xFFFFFFFFu;
   }
-  const int b1 = kTopkBins - 1 - 2 * static_cast<int>(threadIdx.x), b2 = b1 - 1;
-  const uint32_t c1 = sc->hist[level][b1], c2 = sc->hist[level][b2];
+  const int per = (nbins + static_cast<int>(blockDim.x) - 1) / static_cast<int>(blockDim.x);
+  const int top = nbins - 1 - static_cast<int>(threadIdx.x) * per;  // my bins: top, top-1, ..., top-per+1
+  uint32_t mine = 0;
+  for (int j = 0; j < per; ++j)
+    if (top - j >= 0) mine += hist[top - j];
   uint32_t total;
-  const uint32_t above = block_excl_scan(c1 + c2, wsum, total);  // count in bins above b1
-  if (above < need && above + c1 >= need) {
-    s_digit = b1;
-    s_cum = above;
-  } else if (above + c1 < need && above + c1 + c2 >= need) {
-    s_digit = b2;
-    s_cum = above + c1;
+  uint32_t above = block_excl_scan(mine, wsum, total);  // count in bins above my run
+  for (int j = 0; j < per; ++j) {
+    const int bin = top - j;
+    if (bin < 0) break;
+    const uint32_t c = hist[bin];
+    if (above < need && above + c >= need) {
+      s_digit = static_cast<uint32_t>(bin);
+      s_cum = above;
+    }
+    above += c;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
     uint32_t digit = s_digit, cum = s_cum;
     if (cum == 0xFFFFFFFFu) {  // fewer than `need` elements in total: take everything
       digit = 0;
-      cum = total - sc->hist[level][0];
+      cum = total - hist[0];
     }
-    const uint32_t prefix = level == 0 ? digit : level == 1 ? ((old_prefix << 11) | digit) : ((old_prefix << 9) | digit);
+    const uint32_t prefix = level == 0 ? digit : ((old_prefix << 9) | digit);
     sc->st.prefix = prefix;
     sc->st.need = need - cum;  // elements still to take from inside the chosen bin
     if (level == 2) {
       sc->st.threshold = prefix;
       sc->st.need_eq = need - cum;
     }
+    __threadfence();
   }
+  __syncthreads();
 }
 
-// Blocks own contiguous ranges so that compaction preserves index order.
-__device__ __forceinline__ void block_range(int64_t n, int nblocks, int b, int64_t& lo, int64_t& hi) {
+// True in exactly one block of the grid: the one that finishes last.  All blocks' global writes
+// made before the call are visible to that block afterwards.
+__device__ __forceinline__ bool last_block_done(uint32_t* ticket) {
+  __shared__ bool s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (s_last) __threadfence();
+  return s_last;
+}
+
+// Pass 1.  a = g + e, e = a, histogram of the top digit; the last block picks the digit.
+// kVec: 16-byte accesses (all three arrays 16-byte aligned); otherwise element-wise.
+template <bool kBf16, bool kVec>
+__global__ void __launch_bounds__(512) topk_adjust_hist_kernel(const void* __restrict__ grad,
+                                                               float* __restrict__ res, int64_t n,
+                                                               TopkScratch* sc, uint32_t k) {
+  extern __shared__ uint32_t sh[];  // kTopkBins0 counters
+  for (int i = threadIdx.x; i < kTopkBins0; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t tid0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (kVec) {
+    const int64_t nv = n / 4;
+    for (int64_t v = tid0; v < nv; v += stride) {
+      float4 r = reinterpret_cast<const float4*>(res)[v];
+      float g0, g1, g2, g3;
+      if (kBf16) {
+        const uint2 raw = reinterpret_cast<const uint2*>(grad)[v];
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        g0 = __low2float(lo); g1 = __high2float(lo); g2 = __low2float(hi); g3 = __high2float(hi);
+      } else {
+        const float4 g = reinterpret_cast<const float4*>(grad)[v];
+        g0 = g.x; g1 = g.y; g2 = g.z; g3 = g.w;
+      }
+      r.x += g0; r.y += g1; r.z += g2; r.w += g3;
+      reinterpret_cast<float4*>(res)[v] = r;
+      atomicAdd(&sh[digit_of(mag_key(r.x), 0)], 1u);
+      atomicAdd(&sh[digit_of(mag_key(r.y), 0)], 1u);
+      atomicAdd(&sh[digit_of(mag_key(r.z), 0)], 1u);
+      atomicAdd(&sh[digit_of(mag_key(r.w), 0)], 1u);
+    }
+  }
+  for (int64_t i = (kVec ? n / 4 * 4 : 0) + tid0; i < n; i += stride) {
+    float g = kBf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(grad)[i])
+                    : static_cast<const float*>(grad)[i];
+    float a = g + res[i];
+    res[i] = a;
+    atomicAdd(&sh[digit_of(mag_key(a), 0)], 1u);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < kTopkBins0; i += blockDim.x)
+    if (sh[i]) atomicAdd(&sc->hist0[i], sh[i]);
+  if (last_block_done(&sc->st.ticket[0])) pick_bin_block(sc, sc->hist0, kTopkBins0, 0, k);
+}
+
+// Blocks own contiguous ranges (multiples of 4096 elements) so that compaction preserves index order.
+__host__ __device__ __forceinline__ int64_t block_span(int64_t n, int nblocks) {
   int64_t per = (n + nblocks - 1) / nblocks;
-  per = (per + 1023) / 1024 * 1024;
+  return (per + 4095) / 4096 * 4096;
+}
+__device__ __forceinline__ void block_range(int64_t n, int nblocks, int b, int64_t& lo, int64_t& hi) {
+  const int64_t per = block_span(n, nblocks);
   lo = static_cast<int64_t>(b) * per;
   hi = lo + per;
   if (lo > n) lo = n;
   if (hi > n) hi = n;
 }
 
-__global__ void __launch_bounds__(1024) topk_count_blocks_kernel(const float* __restrict__ res, int64_t n,
-                                                                 TopkScratch* sc) {
+// Pass 2.  One read of the residual: counts, per block, the elements above the chosen top-digit bin
+// (selected for sure) and appends the elements INSIDE the bin, as (index, key) pairs, to a
+// candidate list; the remaining 18 bits of the threshold are then found on that short list instead
+// of on two more passes over the whole vector.  The last block does that refinement, turns the
+// candidates into exact per-block counts of selected and tied elements and scans them.  If the bin
+// holds more elements than the list can take (heavily tied data), `overflow` is set and the
+// full-vector refinement kernels below take over.
+constexpr int kStageCap = 2048;  // candidates a block collects in shared memory before one global append
+
+__global__ void __launch_bounds__(1024) topk_collect_refine_kernel(const float* __restrict__ res, int64_t n,
+                                                                   TopkScratch* sc, uint2* __restrict__ cand,
+                                                                   uint32_t cap, uint32_t k) {
+  __shared__ uint32_t s_gt, s_cnt, s_base;
+  __shared__ uint2 stage[kStageCap];
+  __shared__ uint32_t sh_hist[kTopkBins12];
+  __shared__ uint32_t sh_gt[kTopkMaxBlocks], sh_eq[kTopkMaxBlocks];
+  __shared__ uint32_t wsum[33];
+  if (threadIdx.x == 0) s_gt = s_cnt = 0;
+  __syncthreads();
+  const uint32_t b0 = sc->st.prefix;
+  int64_t lo, hi;
+  block_range(n, gridDim.x, blockIdx.x, lo, hi);
+  uint32_t gt = 0;
+  const int lane = threadIdx.x & 31;
+  const bool vec = (reinterpret_cast<uintptr_t>(res) & 15) == 0;
+  // Candidates go to the shared staging list first (one shared atomic per warp and element slot) and
+  // from there to the global list in bulk (one global atomic per flush), so the global counter is
+  // touched a few times per block instead of once per warp and iteration.
+  auto flush = [&]() {
+    __syncthreads();
+    const uint32_t cnt = s_cnt < kStageCap ? s_cnt : kStageCap;
+    if (threadIdx.x == 0 && cnt) s_base = atomicAdd(&sc->st.ncand, cnt);
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < cnt; i += blockDim.x) {
+      const uint32_t pos = s_base + i;
+      if (pos < cap) cand[pos] = stage[i];
+      else sc->st.overflow = 1u;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) s_cnt = 0;
+    __syncthreads();
+  };
+  // the next tile's elements are loaded before this tile's barriers, so the load latency hides
+  // behind the ballots and the block synchronisation
+  auto load_tile = [&](int64_t t0, float* a) {
+    const int64_t i0 = t0 + static_cast<int64_t>(threadIdx.x) * 4;
+    a[0] = a[1] = a[2] = a[3] = 0.f;
+    if (vec && i0 + 4 <= hi) {
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(res + i0));
+      a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (i0 + j < hi) a[j] = res[i0 + j];
+    }
+  };
+  float nxt[4];
+  if (lo < hi) load_tile(lo, nxt);
+  for (int64_t t0 = lo; t0 < hi; t0 += 4096) {
+    const int64_t i0 = t0 + static_cast<int64_t>(threadIdx.x) * 4;
+    float a[4] = {nxt[0], nxt[1], nxt[2], nxt[3]};
+    if (t0 + 4096 < hi) load_tile(t0 + 4096, nxt);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t key = mag_key(a[j]);
+      const uint32_t d = key >> 18;
+      const bool in = i0 + j < hi;
+      gt += in && d > b0;
+      const bool inbin = in && d == b0;
+      const uint32_t m = __ballot_sync(0xFFFFFFFFu, inbin);
+      if (m != 0u) {
+        const int leader = __ffs(m) - 1;
+        uint32_t base = 0;
+        if (lane == leader) base = atomicAdd(&s_cnt, __popc(m));
+        base = __shfl_sync(0xFFFFFFFFu, base, leader);
+        if (inbin) {
+          const uint32_t pos = base + __popc(m & ((1u << lane) - 1u));
+          const uint2 e = make_uint2(static_cast<uint32_t>(i0 + j), key);
+          if (pos < kStageCap) {
+            stage[pos] = e;
+          } else {  // more than the staging list holds within one tile: append directly (rare)
+            const uint32_t gp = atomicAdd(&sc->st.ncand, 1u);
+            if (gp < cap) cand[gp] = e;
+            else sc->st.overflow = 1u;
+          }
+        }
+      }
+    }
+    __syncthreads();
+    if (s_cnt > kStageCap / 2) flush();  // uniform across the block: s_cnt is read after the barrier
+  }
+  flush();
+  for (int o = 16; o > 0; o >>= 1) gt += __shfl_down_sync(0xFFFFFFFFu, gt, o);
+  if (lane == 0 && gt) atomicAdd(&s_gt, gt);
+  __syncthreads();
+  if (threadIdx.x == 0) sc->blk_gt[blockIdx.x] = s_gt;
+  if (!last_block_done(&sc->st.ticket[1])) return;
+
+  // ---- refinement on the candidate list (one block) ----------------------------------------------
+  if (*reinterpret_cast<volatile uint32_t*>(&sc->st.overflow) != 0u) return;
+  const uint32_t nc = *reinterpret_cast<volatile uint32_t*>(&sc->st.ncand);
+  for (int level = 1; level <= 2; ++level) {
+    for (int i = threadIdx.x; i < kTopkBins12; i += blockDim.x) sh_hist[i] = 0;
+    __syncthreads();
+    const uint32_t prefix = sc->st.prefix;
+    for (uint32_t c = threadIdx.x; c < nc; c += blockDim.x) {
+      const uint32_t key = __ldcg(&cand[c].y);
+      if (prefix_matches(key, level, prefix)) atomicAdd(&sh_hist[digit_of(key, level)], 1u);
+    }
+    __syncthreads();
+    pick_bin_block(sc, sh_hist, kTopkBins12, level, k);
+  }
+  const uint32_t T = sc->st.threshold;
+  for (int i = threadIdx.x; i < kTopkMaxBlocks; i += blockDim.x) sh_gt[i] = sh_eq[i] = 0;
+  __syncthreads();
+  const int64_t span = block_span(n, gridDim.x);
+  for (uint32_t c = threadIdx.x; c < nc; c += blockDim.x) {
+    const uint2 e = __ldcg(&cand[c]);
+    const int b = static_cast<int>(e.x / span);
+    if (e.y > T) atomicAdd(&sh_gt[b], 1u);
+    else if (e.y == T) atomicAdd(&sh_eq[b], 1u);
+  }
+  __syncthreads();
+  // one block per thread: totals and exclusive offsets (gridDim.x <= kTopkMaxBlocks == blockDim.x)
+  const int b = threadIdx.x;
+  const bool live = b < static_cast<int>(gridDim.x);
+  const uint32_t g = live ? __ldcg(&sc->blk_gt[b]) + sh_gt[b] : 0u;
+  const uint32_t e = live ? sh_eq[b] : 0u;
+  uint32_t tot;
+  const uint32_t og = block_excl_scan(g, wsum, tot);
+  const uint32_t oe = block_excl_scan(e, wsum, tot);
+  if (live) {
+    sc->blk_gt[b] = g;
+    sc->blk_eq[b] = e;
+    sc->off_gt[b] = og;
+    sc->off_eq[b] = oe;
+  }
+}
+
+// ---- full-vector refinement: only does work when the candidate list overflowed -------------------
+__global__ void __launch_bounds__(512) topk_hist_level_kernel(const float* __restrict__ res, int64_t n,
+                                                              TopkScratch* sc, int level, uint32_t k) {
+  if (sc->st.overflow == 0u) return;
+  __shared__ uint32_t sh[kTopkBins12];
+  for (int i = threadIdx.x; i < kTopkBins12; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  const uint32_t prefix = sc->st.prefix;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    uint32_t key = mag_key(res[i]);
+    if (prefix_matches(key, level, prefix)) atomicAdd(&sh[digit_of(key, level)], 1u);
+  }
+  __syncthreads();
+  uint32_t* h = hist_of(sc, level);
+  for (int i = threadIdx.x; i < kTopkBins12; i += blockDim.x)
+    if (sh[i]) atomicAdd(&h[i], sh[i]);
+  if (last_block_done(&sc->st.ticket[1 + level])) pick_bin_block(sc, h, kTopkBins12, level, k);
+}
+
+__global__ void __launch_bounds__(1024) topk_count_scan_kernel(const float* __restrict__ res, int64_t n,
+                                                               TopkScratch* sc) {
+  if (sc->st.overflow == 0u) return;
   __shared__ uint32_t s_gt, s_eq;
+  __shared__ uint32_t wsum[33];
   if (threadIdx.x == 0) s_gt = s_eq = 0;
   __syncthreads();
   const uint32_t T = sc->st.threshold;
@@ -199,22 +394,25 @@ __global__ void __launch_bounds__(1024) topk_count_blocks_kernel(const float* __
     sc->blk_gt[blockIdx.x] = s_gt;
     sc->blk_eq[blockIdx.x] = s_eq;
   }
-}
-
-__global__ void topk_scan_blocks_kernel(TopkScratch* sc, int nblocks) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  uint32_t g = 0, e = 0;
-  for (int b = 0; b < nblocks; ++b) {
-    sc->off_gt[b] = g;
-    sc->off_eq[b] = e;
-    g += sc->blk_gt[b];
-    e += sc->blk_eq[b];
+  if (!last_block_done(&sc->st.ticket[4])) return;
+  const int b = threadIdx.x;
+  const bool live = b < static_cast<int>(gridDim.x);
+  const uint32_t g = live ? __ldcg(&sc->blk_gt[b]) : 0u;
+  const uint32_t e = live ? __ldcg(&sc->blk_eq[b]) : 0u;
+  uint32_t tot;
+  const uint32_t og = block_excl_scan(g, wsum, tot);
+  const uint32_t oe = block_excl_scan(e, wsum, tot);
+  if (live) {
+    sc->off_gt[b] = og;
+    sc->off_eq[b] = oe;
   }
 }
 
+// Pass 3.  Ordered compaction: every thread owns 4 consecutive elements, one block-wide scan per
+// 4096 elements gives each selected element its position in the index-sorted output.
 __global__ void __launch_bounds__(1024) topk_compact_kernel(float* __restrict__ res, int64_t n, TopkScratch* sc,
                                                             uint2* __restrict__ pairs, uint32_t k) {
-  __shared__ uint32_t ws_a[33], ws_b[33];
+  __shared__ uint32_t ws_a[33];
   const uint32_t T = sc->st.threshold;
   const uint32_t need_eq = sc->st.need_eq;
   int64_t lo, hi;
@@ -222,27 +420,69 @@ __global__ void __launch_bounds__(1024) topk_compact_kernel(float* __restrict__ 
   uint32_t eq_base = sc->off_eq[blockIdx.x];
   // selected elements that precede this block
   uint32_t out_base = sc->off_gt[blockIdx.x] + (eq_base < need_eq ? eq_base : need_eq);
-  for (int64_t t0 = lo; t0 < hi; t0 += blockDim.x) {
-    const int64_t i = t0 + threadIdx.x;
-    float a = 0.f;
-    uint32_t key = 0;
-    bool in = i < hi;
-    if (in) {
-      a = res[i];
-      key = mag_key(a);
+  const bool vec = (reinterpret_cast<uintptr_t>(res) & 15) == 0;
+  auto load_tile = [&](int64_t t0, float* a) {
+    const int64_t i0 = t0 + static_cast<int64_t>(threadIdx.x) * 4;
+    a[0] = a[1] = a[2] = a[3] = 0.f;
+    if (vec && i0 + 4 <= hi) {
+      const float4 v = *reinterpret_cast<const float4*>(res + i0);
+      a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (i0 + j < hi) a[j] = res[i0 + j];
     }
-    const uint32_t is_eq = in && key == T;
-    uint32_t eq_total;
-    const uint32_t eq_rank = eq_base + block_excl_scan(is_eq, ws_a, eq_total);
-    const uint32_t sel = in && (key > T || (is_eq && eq_rank < need_eq));
-    uint32_t sel_total;
-    const uint32_t pos = out_base + block_excl_scan(sel, ws_b, sel_total);
-    if (sel && pos < k) {
-      pairs[pos] = make_uint2(static_cast<uint32_t>(i), __float_as_uint(a));
-      res[i] = 0.f;  // sent: nothing left to feed back for this entry
+  };
+  float nxt[4];
+  if (lo < hi) load_tile(lo, nxt);
+  for (int64_t t0 = lo; t0 < hi; t0 += 4096) {
+    const int64_t i0 = t0 + static_cast<int64_t>(threadIdx.x) * 4;
+    float a[4] = {nxt[0], nxt[1], nxt[2], nxt[3]};
+    if (t0 + 4096 < hi) load_tile(t0 + 4096, nxt);  // in flight during this tile's scan
+    uint32_t gt[4], eq[4], ngt = 0, neq = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t key = mag_key(a[j]);
+      const bool in = i0 + j < hi;
+      gt[j] = in && key > T;
+      eq[j] = in && key == T;
+      ngt += gt[j];
+      neq += eq[j];
     }
-    eq_base += eq_total;
-    out_base += sel_total;
+    // one scan of both counts: at most 4096 of each per tile, so 16 bits apiece are enough
+    uint32_t total;
+    const uint32_t ex = block_excl_scan((ngt << 16) | neq, ws_a, total);
+    uint32_t my_gt = ex >> 16, my_eq = eq_base + (ex & 0xFFFFu);
+    const uint32_t eq_taken_before_tile = eq_base < need_eq ? eq_base : need_eq;
+    bool wrote = false;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const bool sel = gt[j] || (eq[j] && my_eq < need_eq);
+      if (sel) {
+        const uint32_t eq_taken = my_eq < need_eq ? my_eq : need_eq;
+        const uint32_t pos = out_base + my_gt + (eq_taken - eq_taken_before_tile);
+        if (pos < k) {
+          pairs[pos] = make_uint2(static_cast<uint32_t>(i0 + j), __float_as_uint(a[j]));
+          a[j] = 0.f;  // sent: nothing left to feed back for this entry
+          wrote = true;
+        }
+      }
+      my_gt += gt[j];
+      my_eq += eq[j];
+    }
+    if (wrote) {
+      if (vec && i0 + 4 <= hi) {
+        *reinterpret_cast<float4*>(res + i0) = make_float4(a[0], a[1], a[2], a[3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (i0 + j < hi) res[i0 + j] = a[j];
+      }
+    }
+    const uint32_t t_gt = total >> 16, t_eq = total & 0xFFFFu;
+    const uint32_t eq_after = eq_base + t_eq;
+    out_base += t_gt + ((eq_after < need_eq ? eq_after : need_eq) - eq_taken_before_tile);
+    eq_base = eq_after;
   }
 }
 
@@ -369,23 +609,28 @@ size_t topk_scratch_bytes() { return sizeof(TopkScratch); }
 cudaError_t launch_topk_select(const TopkArgs& a, cudaStream_t s) {
   if (a.n <= 0 || a.k <= 0 || a.k > a.n) return cudaErrorInvalidValue;
   TopkScratch* sc = static_cast<TopkScratch*>(a.scratch);
-  note_launch(10);
+  const uint32_t k = static_cast<uint32_t>(a.k);
+  note_launch(7);
   const int grid = static_cast<int>(std::min<int64_t>((a.n + 4095) / 4096, 148 * 4));
+  const bool vec = ((reinterpret_cast<uintptr_t>(a.grad) | reinterpret_cast<uintptr_t>(a.residual)) & 15) == 0;
+  const size_t smem = kTopkBins0 * sizeof(uint32_t);
   topk_clear_kernel<<<8, 256, 0, s>>>(sc);
-  if (a.grad_is_bf16)
-    topk_adjust_hist_kernel<true><<<grid, 512, 0, s>>>(a.grad, a.residual, a.n, sc);
-  else
-    topk_adjust_hist_kernel<false><<<grid, 512, 0, s>>>(a.grad, a.residual, a.n, sc);
-  topk_pick_bin_kernel<<<1, 1024, 0, s>>>(sc, 0, static_cast<uint32_t>(a.k));
-  topk_hist_level_kernel<<<grid, 512, 0, s>>>(a.residual, a.n, sc, 1);
-  topk_pick_bin_kernel<<<1, 1024, 0, s>>>(sc, 1, static_cast<uint32_t>(a.k));
-  topk_hist_level_kernel<<<grid, 512, 0, s>>>(a.residual, a.n, sc, 2);
-  topk_pick_bin_kernel<<<1, 1024, 0, s>>>(sc, 2, static_cast<uint32_t>(a.k));
+  if (a.grad_is_bf16) {
+    if (vec) topk_adjust_hist_kernel<true, true><<<grid, 512, smem, s>>>(a.grad, a.residual, a.n, sc, k);
+    else topk_adjust_hist_kernel<true, false><<<grid, 512, smem, s>>>(a.grad, a.residual, a.n, sc, k);
+  } else {
+    if (vec) topk_adjust_hist_kernel<false, true><<<grid, 512, smem, s>>>(a.grad, a.residual, a.n, sc, k);
+    else topk_adjust_hist_kernel<false, false><<<grid, 512, smem, s>>>(a.grad, a.residual, a.n, sc, k);
+  }
   const int nb = select_blocks(a.n);
-  topk_count_blocks_kernel<<<nb, 1024, 0, s>>>(a.residual, a.n, sc);
-  topk_scan_blocks_kernel<<<1, 32, 0, s>>>(sc, nb);
-  topk_compact_kernel<<<nb, 1024, 0, s>>>(a.residual, a.n, sc, static_cast<uint2*>(a.pairs),
-                                          static_cast<uint32_t>(a.k));
+  // The output buffer doubles as the candidate list: it is only written for good by the last pass.
+  topk_collect_refine_kernel<<<nb, 1024, 0, s>>>(a.residual, a.n, sc, static_cast<uint2*>(a.pairs), k, k);
+  // heavily tied data only (these return at once otherwise; one CTA per SM keeps the idle launch cheap)
+  const int fgrid = grid < 148 ? grid : 148;
+  topk_hist_level_kernel<<<fgrid, 512, 0, s>>>(a.residual, a.n, sc, 1, k);
+  topk_hist_level_kernel<<<fgrid, 512, 0, s>>>(a.residual, a.n, sc, 2, k);
+  topk_count_scan_kernel<<<nb, 1024, 0, s>>>(a.residual, a.n, sc);
+  topk_compact_kernel<<<nb, 1024, 0, s>>>(a.residual, a.n, sc, static_cast<uint2*>(a.pairs), k);
   return cudaGetLastError();
 }
 

@@ -5,6 +5,13 @@
 //            radix select on the magnitude bits, ties to the lower index);
 //            emit them as (u32 index, f32 value) pairs sorted by index;
 //            e = a with the k selected entries zeroed          (topk_select)
+//            Three passes over the data: adjust + 13-bit histogram (12 B per
+//            fp32 element), collect (4 B: per-block counts of the elements
+//            above the chosen bin, the elements inside it go to a candidate
+//            list on which the remaining 18 bits are resolved), ordered
+//            compaction (4 B).  Only if the bin holds more than k elements
+//            (heavily tied data) two more full histogram passes and a count
+//            pass run instead of the candidate refinement.
 //   exchange every rank pushes its k pairs into slot[rank] of every peer's
 //            arena over NVLink, release flag                    (exchange)
 //   scatter  dense = scale * sum_r sparse_r, written into g: each CTA owns a
@@ -25,7 +32,8 @@ namespace mccl {
 namespace kern {
 
 constexpr int kTopkMaxBlocks = 1024;   // blocks of the ordered compaction
-constexpr int kTopkBins = 2048;        // bins of one radix level
+constexpr int kTopkBins0 = 8192;       // bins of the first radix level (13 magnitude bits)
+constexpr int kTopkBins12 = 512;       // bins of the second and third level (9 bits each)
 
 struct TopkArgs {
   const void* grad;     // n elements, fp32 or bf16; overwritten with the dense result by scatter
@@ -38,7 +46,7 @@ struct TopkArgs {
   float scale;          // applied in scatter
 };
 
-// Scratch layout: 3 histograms, the selection state, per-block counts/offsets.
+// Scratch layout: 3 histograms, the selection state, per-block counts/offsets (about 53 KB).
 size_t topk_scratch_bytes();
 #ifdef __CUDACC__
 __host__ __device__

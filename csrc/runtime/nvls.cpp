@@ -190,8 +190,11 @@ bool NvlsRegion::device_supported(std::string* why) {
 }
 
 std::unique_ptr<NvlsRegion> NvlsRegion::create(int rank, int ws, size_t buffer_bytes, int nbuffers,
-                                               const std::string& uid_hint, const Exchange& exchange,
+                                               const std::string& uid_hint, const Exchange& exchange_raw,
                                                std::string* why) {
+  const Exchange exchange = [&](const std::string& tag, const std::string& mine) {
+    return exchange_raw(uid_hint + "/" + tag, mine);
+  };
   std::unique_ptr<NvlsRegion> reg(new NvlsRegion());
   reg->impl_ = std::make_unique<Impl>();
   Impl& im = *reg->impl_;
@@ -232,7 +235,6 @@ std::unique_ptr<NvlsRegion> NvlsRegion::create(int rank, int ws, size_t buffer_b
     o << uid_hint << "-" << getpid() << "-" << counter.fetch_add(1) << "-" << std::hex << rd();
     uid = o.str();
   }
-  std::vector<std::string> all;
   {
     std::vector<std::string> got = exchange("nvls_uid", (e.empty() ? "ok" : "E" + e) + std::string("|") + uid);
     std::string bad;
@@ -390,6 +392,24 @@ void NvlsRegion::release() {
   if (prev >= 0) cudaSetDevice(prev);
   impl_.reset();
 }
+
+void NvlsRegion::release_multicast_keep_memory() {
+  if (!impl_) return;
+  Impl& im = *impl_;
+  int prev = -1;
+  cudaGetDevice(&prev);
+  cudaSetDevice(im.device);
+  if (im.mc_mapped) im.d.MemUnmap(im.mc_va, im.total);
+  if (im.mc_va) im.d.MemAddressFree(im.mc_va, im.total);
+  if (im.bound) im.d.MulticastUnbind(im.mc_handle, im.cudev, 0, im.total);
+  if (im.have_mc) im.d.MemRelease(im.mc_handle);
+  im.mc_mapped = im.bound = im.have_mc = false;
+  im.mc_va = 0;
+  mc_ = nullptr;
+  if (prev >= 0) cudaSetDevice(prev);
+}
+
+size_t NvlsRegion::total_bytes() const { return impl_ ? impl_->total : 0; }
 
 NvlsRegion::~NvlsRegion() { release(); }
 

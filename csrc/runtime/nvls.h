@@ -39,13 +39,18 @@ class NvlsRegion {
 
   // Collective.  `buffer_bytes` per buffer, `nbuffers` buffers per rank; the current CUDA device is
   // used.  Returns nullptr and fills `why` when NVLS is unavailable or any rank failed.
+  // `tag`: distinguishes several regions created through the same exchange (it prefixes the keys).
   static std::unique_ptr<NvlsRegion> create(int rank, int world_size, size_t buffer_bytes, int nbuffers,
-                                            const std::string& uid, const Exchange& exchange, std::string* why);
+                                            const std::string& tag, const Exchange& exchange, std::string* why);
   // Cheap local test: does this device report multicast support (and can the entry points be resolved)?
   static bool device_supported(std::string* why);
 
   ~NvlsRegion();
   void release();  // idempotent; unmap + unbind + free
+  // Ends the multicast side only (unmap the multicast alias, unbind, drop the object) and keeps this
+  // rank's own memory mapped: for regions that hold tensors which may outlive the process group.
+  void release_multicast_keep_memory();
+  size_t total_bytes() const;
 
   char* uc() const { return uc_; }
   char* mc() const { return mc_; }

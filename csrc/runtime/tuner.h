@@ -48,11 +48,15 @@ class Tuner {
         // costs more: 160 us vs 153 us).
         oneshot_max_[ws][cls] = ws <= 2 ? (int64_t(32) << 20) : ws <= 4 ? (int64_t(4) << 20) : (int64_t(1) << 20);
         // NVLS moves (1 + 1/ws) * N per direction instead of 2 (ws-1)/ws * N: no gain at 2 ranks,
-        // 1.2x at 4 and 1.55x at 8, and it pays two local staging passes; used above the one-shot range.
-        nvls_min_[ws][cls] = ws <= 2 ? kNever : ws <= 4 ? (int64_t(8) << 20) : (int64_t(1) << 20) + 1;
+        // 1.2x at 4 and 1.55x at 8, and it pays two local staging passes.  Measured on 4 ranks: equal to
+        // the two-shot kernel within noise from 16 MiB to 1 GiB (231 vs 235 us at 64 MiB), so it is only
+        // used from 5 ranks on, above the one-shot range.
+        nvls_min_[ws][cls] = ws <= 4 ? kNever : (int64_t(1) << 20) + 1;
       }
-      ag_nvls_min_[ws] = ws <= 2 ? kNever : (int64_t(256) << 10);
-      bc_nvls_min_[ws] = ws <= 2 ? kNever : (int64_t(256) << 10);
+      // multimem.st also delivers a copy back to the sender, which costs 1/ws of the ingress: measured on
+      // 4 ranks the plain peer stores win at every size (1 GiB allgather: 1.37 ms vs 1.89 ms)
+      ag_nvls_min_[ws] = kNever;
+      bc_nvls_min_[ws] = kNever;
       ctas_small_[ws] = 32;
       ctas_large_[ws] = kern::kMaxCtasPerLane;  // two lanes may run at once: 2 x 64 CTAs stay below the 148 SMs
       // measured on 2 ranks: 64 MiB 158 us pushed vs 185 us pulled (the stores overlap the reduction)
@@ -104,6 +108,7 @@ class Tuner {
     const int cap = overlapped && ctas_overlap_[ws] > 0 ? ctas_overlap_[ws] : ctas_large_[ws];
     return kern::pick_ctas(pushed_bytes, ws, cap);
   }
+  void set_ctas_overlap(int ws, int v) { ctas_overlap_[ws] = v < kern::kMaxCtasPerLane ? v : kern::kMaxCtasPerLane; }
   void set_ctas(int ws, int small, int large) {
     if (small > 0) ctas_small_[ws] = small;
     if (large > 0) ctas_large_[ws] = large;
@@ -186,7 +191,9 @@ class Tuner {
   int push_gather_[kern::kMaxWorld + 1];
   int ctas_overlap_[kern::kMaxWorld + 1];
   size_t segment_bytes_ = size_t(64) << 20;
-  int mover_tile_bytes_ = 128 << 10;
+  // measured on 2 ranks (64 MiB broadcast: 160 us with 128 KiB tiles, 132 us with 512 KiB, 117 us with
+  // 2 MiB; 16 MiB allgather: 34 / 35 / 49 us): every tile costs a system-scope fence on the sender
+  int mover_tile_bytes_ = 1 << 20;
   int nvls_tile_bytes_ = 0;  // 0: kernel default
   int64_t nvls_split_min_bytes_ = int64_t(8) << 20;
 };

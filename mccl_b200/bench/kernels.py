@@ -79,32 +79,140 @@ def bench_twoshot(native, n, iters, ws=4):
     return ms, per_rank * ws, f"emulated {ws} ranks on one GPU: all push/reduce/pull traffic is local HBM"
 
 
+def bench_oneshot(native, n, iters, ws=4):
+    n = min(n, 1 << 20)  # the one-shot kernel is the small-message variant
+    grp = native.EmuGroup(ws, max(n * 4 * ws * 2, 8 << 20))
+    ts = [torch.randn(n, device="cuda") for _ in range(ws)]
+
+    def run():
+        grp.allreduce(ts, "sum", "oneshot", "none", 1.0, 16)
+    ms = timeit(run, iters)
+    # per rank: reads N, writes (ws-1) N into the peers' slots, reads ws N back, writes N
+    return ms, n * 4 * (1 + (ws - 1) + ws + 1) * ws, f"emulated {ws} ranks on one GPU (one-shot: push to every peer, reduce ws slots)"
+
+
+def bench_allgather(native, n, iters, ws=4):
+    per = n // ws
+    grp = native.EmuGroup(ws, max(per * 4 * ws * 2, 8 << 20))
+    ins = [torch.randn(per, device="cuda") for _ in range(ws)]
+    outs = [torch.empty(per * ws, device="cuda") for _ in range(ws)]
+
+    def run():
+        grp.allgather(outs, ins, 16)
+    ms = timeit(run, iters)
+    # per rank: reads its block, stores it ws-1 times remotely + once locally, copies ws-1 blocks out (read + write)
+    return ms, per * 4 * (1 + ws + 2 * (ws - 1)) * ws, f"emulated {ws} ranks on one GPU (push + per-tile flags + copy-out)"
+
+
+def bench_broadcast(native, n, iters, ws=4):
+    grp = native.EmuGroup(ws, max(n * 4 * 2, 8 << 20))
+    ts = [torch.randn(n, device="cuda") for _ in range(ws)]
+
+    def run():
+        grp.broadcast(ts, 0, 16)
+    ms = timeit(run, iters)
+    # two hops: root reads N and stores N; each owner re-reads its slice, stores it ws-2 times and once to its tensor;
+    # every non-root copies the other slices out (read + write)
+    nr = ws - 1
+    total = n * 4 * (2 + nr * (1.0 / nr) * (1 + (ws - 2) + 1) + nr * 2.0 * (nr - 1) / nr)
+    return ms, total, f"emulated {ws} ranks on one GPU (two-hop push broadcast)"
+
+
+def bench_reduce_scatter(native, n, iters, ws=4):
+    per = n // ws
+    grp = native.EmuGroup(ws, max(per * 4 * ws * 2 + 4096, 8 << 20))
+    ins = [torch.randn(per * ws, device="cuda") for _ in range(ws)]
+    outs = [torch.empty(per, device="cuda") for _ in range(ws)]
+
+    def run():
+        grp.reduce_scatter(outs, ins, "sum", 16, 0)
+    ms = timeit(run, iters)
+    # per rank: reads (ws-1) chunks and stores them remotely, then reads ws-1 slots + own chunk and writes one chunk
+    return ms, per * 4 * (2 * (ws - 1) + ws + 1) * ws, f"emulated {ws} ranks on one GPU (push + rank-ordered reduction)"
+
+
+def bench_topk_exchange(native, n, iters, ws=4):
+    n = min(n, 16 << 20)
+    grp = native.EmuGroup(ws, 32 << 20)
+    gs = [torch.randn(n, device="cuda") for _ in range(ws)]
+    rs = [torch.zeros(n, device="cuda") for _ in range(ws)]
+
+    def run():
+        grp.topk_allreduce(gs, rs, 0.01, 1.0 / ws, 16)
+    ms = timeit(run, iters)
+    k = max(1, int(n * 0.01))
+    # select (20 B/elem) + pairs pushed to ws ranks + dense zero-fill and sparse adds
+    return ms, (n * 20 + k * 8 * (1 + ws) + n * 4 + k * 8 * ws) * ws, f"emulated {ws} ranks: select + sparse exchange + scatter"
+
+
 def bench_topk(native, n, iters):
     g = torch.randn(n, device="cuda")
     r = torch.zeros(n, device="cuda")
 
     def run():
         native._topk_select(g, r, 0.01)
-    return timeit(run, iters), n * 28, "adjust (12 B) + 2 histogram passes + count + compact (4 B each) per element"
+    return timeit(run, iters), n * 20, "adjust + histogram (12 B) + collect (4 B) + ordered compaction (4 B) per element"
 
 
-def bench_stft(native, n, iters):
+def bench_stft(native, n, iters, n_fft=2048):
     from mccl_b200.transforms import stft
     x = torch.randn(16, n // 16, device="cuda")
-    w = torch.hann_window(2048, device="cuda")
+    w = torch.hann_window(n_fft, device="cuda")
+    hop = n_fft // 4
 
     def run():
-        stft(x, n_fft=2048, hop_length=512, win_length=2048, window=w)
-    frames = 1 + (n // 16) // 512
-    return timeit(run, iters), 16 * frames * (2048 * 4 + 1025 * 8), "frame loads (L2-resident overlap) + spectrum written"
+        stft(x, n_fft=n_fft, hop_length=hop, win_length=n_fft, window=w)
+    frames = 1 + (n // 16) // hop
+    return timeit(run, iters), 16 * frames * (n_fft * 4 + (n_fft // 2 + 1) * 8), "frame loads (L2-resident overlap) + spectrum written"
 
 
-BENCHES = {"adamw": bench_adamw, "ew": bench_ew, "twoshot": bench_twoshot, "topk": bench_topk, "stft": bench_stft}
+def stft_vs_torch(native, n, iters):
+    """Forward and forward+backward of STFT / iSTFT against torch.stft / torch.istft (cuFFT), same box."""
+    from mccl_b200.transforms import istft, stft
+    rows = []
+    for n_fft in (512, 2048, 4096):
+        hop = n_fft // 4
+        w = torch.hann_window(n_fft, device="cuda")
+        x = torch.randn(16, n // 16, device="cuda", requires_grad=True)
+
+        def ours_f():
+            return stft(x, n_fft=n_fft, hop_length=hop, win_length=n_fft, window=w)
+
+        def torch_f():
+            return torch.stft(x, n_fft, hop_length=hop, win_length=n_fft, window=w, center=True, pad_mode="reflect",
+                              return_complex=True)
+
+        def fb(fn):
+            def run():
+                x.grad = None
+                y = fn()
+                torch.view_as_real(y).square().sum().backward()
+            return run
+        spec = ours_f().detach()
+
+        def ours_i():
+            return istft(spec, n_fft=n_fft, hop_length=hop, win_length=n_fft, window=w, length=n // 16)
+
+        def torch_i():
+            return torch.istft(spec, n_fft, hop_length=hop, win_length=n_fft, window=w, center=True, length=n // 16)
+        with torch.no_grad():
+            t = {"stft_fwd_ms": timeit(ours_f, iters), "torch_stft_fwd_ms": timeit(torch_f, iters),
+                 "istft_fwd_ms": timeit(ours_i, iters), "torch_istft_fwd_ms": timeit(torch_i, iters)}
+        t["stft_fwd_bwd_ms"] = timeit(fb(ours_f), iters)
+        t["torch_stft_fwd_bwd_ms"] = timeit(fb(torch_f), iters)
+        rows.append({"kernel": "stft_vs_torch", "n_fft": n_fft, "hop": hop, "batch": 16, "samples": n // 16,
+                     **{k: round(v, 4) for k, v in t.items()}})
+    return rows
+
+
+BENCHES = {"adamw": bench_adamw, "ew": bench_ew, "twoshot": bench_twoshot, "oneshot": bench_oneshot,
+           "allgather": bench_allgather, "broadcast": bench_broadcast, "reduce_scatter": bench_reduce_scatter,
+           "topk": bench_topk, "topk_exchange": bench_topk_exchange, "stft": bench_stft}
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default="all", choices=["all"] + list(BENCHES))
+    ap.add_argument("--kernel", default="all", choices=["all", "stft_vs_torch"] + list(BENCHES))
     ap.add_argument("--elements", type=int, default=64 << 20)
     ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
@@ -112,6 +220,10 @@ def main():
     native = mccl.require_native()
     torch.cuda.set_device(0)
     peak, src = peak_gbs()
+    if args.kernel == "stft_vs_torch":
+        for row in stft_vs_torch(native, args.elements, args.iters):
+            print(json.dumps(row), flush=True)
+        return
     for name in (BENCHES if args.kernel == "all" else [args.kernel]):
         ms, nbytes, what = BENCHES[name](native, args.elements, args.iters)
         gbs = nbytes / (ms * 1e-3) / 1e9

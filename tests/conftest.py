@@ -56,3 +56,35 @@ def pytest_collection_modifyitems(config, items):
         want = need.kwargs.get("count", 1)
         if n < want:
             item.add_marker(pytest.mark.skip(reason=f"needs {want} CUDA device(s), found {n}"))
+
+
+def pytest_terminal_summary(terminalreporter, exitstatus, config):
+    """With ``MCCL_TEST_SUMMARY=<file>``: per-file pass / fail / skip counts, the GPU count and the
+    commit, as JSON (the durable record of a multi-GPU run)."""
+    path = os.environ.get("MCCL_TEST_SUMMARY")
+    if not path:
+        return
+    import json
+    import subprocess
+    per_file = {}
+    for outcome in ("passed", "failed", "skipped", "error"):
+        for rep in terminalreporter.stats.get(outcome, []):
+            nodeid = getattr(rep, "nodeid", "") or ""
+            f = nodeid.split("::")[0]
+            if not f or (outcome != "skipped" and getattr(rep, "when", "call") != "call" and outcome == "passed"):
+                continue
+            per_file.setdefault(f, {"passed": 0, "failed": 0, "skipped": 0, "error": 0})[outcome] += 1
+    try:
+        commit = subprocess.run(["git", "rev-parse", "--short", "HEAD"], capture_output=True, text=True, cwd=str(ROOT)).stdout.strip()
+    except Exception:
+        commit = ""
+    gpus, name = _cuda_count(), ""
+    try:
+        import torch
+        name = torch.cuda.get_device_name(0) if gpus else ""
+    except Exception:
+        pass
+    out = {"gpus": gpus, "gpu_name": name, "commit": commit or os.environ.get("MCCL_COMMIT", ""), "exitstatus": int(exitstatus),
+           "per_file": per_file, "totals": {k: sum(v[k] for v in per_file.values()) for k in ("passed", "failed", "skipped", "error")}}
+    with open(path, "w") as fh:
+        json.dump(out, fh, indent=1, sort_keys=True)

@@ -200,3 +200,81 @@ def test_ddp_with_nvls_auto(ws):
         pytest.skip("not enough GPUs")
     run_workers(_nvls_auto_ddp_worker, ws, device="cuda", timeout=300,
                 env={"MCCL_NVLS": "1", "MCCL_NVLS_MIN_BYTES": "1048577"})
+
+
+def _inplace_worker(rank, ws):
+    import torch, torch.distributed as dist
+    from mccl_b200.parallel.ddp import _nvls_bucket_pool
+    from mccl_b200.parallel import wrap_ddp
+    native = mccl.require_native()
+    be = mccl.get_backend(device=device)
+    dist.all_reduce(torch.ones(8, device=device))
+    if not be.data_plane().endswith("+nvls"):
+        print("NVLS_UNAVAILABLE", flush=True)
+        return
+    # 1. raw tensors from the multicast-bound pool are reduced in place by the switch
+    holder = torch.nn.Linear(4096, 4096).to(device)          # sizes the pool (about 64 MiB x 4 + slack)
+    pool = _nvls_bucket_pool(holder, None)
+    assert pool is not None
+    with torch.cuda.use_mem_pool(pool):
+        bufs = {dt: torch.empty(3_000_000, dtype=dt, device=device) for dt in (torch.float32, torch.bfloat16, torch.float16)}
+        small = torch.empty(1000, device=device)
+    for dt, buf in bufs.items():
+        assert native._nvls_pool_contains(buf)
+        for rep in range(3):
+            g = torch.Generator().manual_seed(rank * 31 + rep)
+            x = torch.randn(buf.numel(), generator=g).to(device).to(dt)
+            ins = [torch.empty_like(x) for _ in range(ws)]
+            dist.all_gather(ins, x)
+            want = torch.stack([i.double() for i in ins]).sum(0)
+            buf.copy_(x)
+            dist.all_reduce(buf, op=dist.ReduceOp.AVG if rep == 1 else dist.ReduceOp.SUM)
+            if rep == 1:
+                want = want / ws
+            tol = 1e-5 if dt == torch.float32 else 3e-2
+            assert (buf.double() - want).abs().max().item() <= tol * max(1.0, want.abs().max().item()) * ws, (dt, rep)
+            outs = [torch.empty_like(buf) for _ in range(ws)]
+            dist.all_gather(outs, buf)
+            for o in outs:
+                assert torch.equal(o, outs[0])
+        # a view whose byte length is not a multiple of 16 takes the staged path and leaves its neighbours alone
+        buf.fill_(1)
+        v = buf[5:5 + 1001]
+        dist.all_reduce(v)
+        assert buf[4].item() == 1 and buf[5].item() == ws and buf[5 + 1000].item() == ws and buf[5 + 1001].item() == 1
+    small.fill_(2.0); dist.all_reduce(small); assert small[0].item() == 2.0 * ws    # below the in-place floor
+    # 2. DDP buckets land in the pool (before and after DDP re-buckets) and training matches one process
+    def make():
+        torch.manual_seed(42)
+        return torch.nn.Sequential(torch.nn.Linear(512, 2048), torch.nn.ReLU(), torch.nn.Linear(2048, 2048),
+                                   torch.nn.ReLU(), torch.nn.Linear(2048, 10)).to(device)
+    ref = make()
+    model = wrap_ddp(make(), device_ids=[device.index], bucket_cap_mb=4)
+    assert getattr(model, "_mccl_nvls_pool", None) is not None
+    opt = torch.optim.SGD(model.parameters(), lr=0.05)
+    ref_opt = torch.optim.SGD(ref.parameters(), lr=0.05)
+    g = torch.Generator().manual_seed(7)
+    for step in range(5):
+        xs = torch.randn(8 * ws, 512, generator=g); ys = torch.randint(0, 10, (8 * ws,), generator=g)
+        opt.zero_grad()
+        torch.nn.functional.cross_entropy(model(xs[rank * 8:(rank + 1) * 8].to(device)), ys[rank * 8:(rank + 1) * 8].to(device)).backward()
+        in_pool = [native._nvls_pool_contains(p.grad) for p in model.module.parameters()]
+        assert all(in_pool), (step, in_pool)
+        opt.step()
+        ref_opt.zero_grad()
+        torch.nn.functional.cross_entropy(ref(xs.to(device)), ys.to(device)).backward()
+        ref_opt.step()
+    for p, q in zip(model.module.parameters(), ref.parameters()):
+        assert torch.allclose(p, q, rtol=1e-4, atol=1e-5), (p - q).abs().max()
+    assert mccl.get_metrics().total_errors == 0
+
+
+@pytest.mark.parametrize("ws", _world_sizes())
+def test_nvls_in_place_allreduce_on_pool_tensors_and_ddp_buckets(ws):
+    if ws > _ngpu():
+        pytest.skip("not enough GPUs")
+    res = run_workers(_inplace_worker, ws, device="cuda", timeout=300,
+                      env={"MCCL_NVLS": "1", "MCCL_LOG_LEVEL": "INFO", "MCCL_DEVICE_TIMING": "1", "MCCL_NVLS_BUCKETS_MIN_WORLD": "2"})
+    _skip_if_unavailable(res)
+    if "NVLS_UNAVAILABLE" not in res[0].stdout:
+        assert "algo=nvls-inplace" in res[0].stderr, res[0].stderr[-2000:]

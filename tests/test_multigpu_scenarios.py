@@ -252,3 +252,26 @@ def _ctas_clamped(rank, ws):
 
 def test_oversized_cta_request_is_clamped_not_timed_out():
     run_workers(_ctas_clamped, 2, device="cuda", timeout=240, env={"MCCL_COMM_CTAS": "128", "MCCL_DEVICE_WAIT_US": "3000000"})
+
+
+def _info_lines(rank, ws):
+    import time
+    import torch, torch.distributed as dist
+    t = torch.ones(2_000_000, device=device); dist.all_reduce(t)
+    t = torch.ones(1000, device=device); dist.all_reduce(t)
+    b = torch.ones(300_000, device=device); dist.broadcast(b, 0)
+    o = torch.empty(1000 * ws, device=device); dist.all_gather_into_tensor(o, torch.ones(1000, device=device))
+    rs = torch.empty(1000, device=device); dist.reduce_scatter_tensor(rs, torch.ones(1000 * ws, device=device))
+    torch.cuda.synchronize()
+    time.sleep(1.2)   # the watchdog poll retires the timed collectives and prints their lines
+
+
+def test_one_info_line_per_collective_with_variant_time_and_busbw():
+    import re
+    res = run_workers(_info_lines, 2, device="cuda", timeout=240,
+                      env={"MCCL_LOG_LEVEL": "INFO", "MCCL_DEVICE_TIMING": "1"})
+    err = res[0].stderr
+    for name, algo in (("mccl:all_reduce", "twoshot|oneshot|nvls"), ("mccl:broadcast", "direct|twohop|nvls"),
+                       ("mccl:all_gather", "push"), ("mccl:reduce_scatter", ".*")):
+        pat = re.compile(rf"{name} seq=\d+ algo=({algo})\S* bytes=\d+ device_us=[0-9.]+ busbw=[0-9.]+ GB/s")
+        assert pat.search(err), f"no INFO line for {name}:\n{err[-3000:]}"

@@ -86,3 +86,15 @@ def test_tile_plan_is_a_partition_owned_by_cta_index(native):
                 assert (nt - 1) * tu < units <= nt * tu
                 per_cta = -(-nt // nctas)
                 assert per_cta <= 1024, "12-bit tile counters"
+
+
+def test_pool_range_allocator_first_fit_and_coalescing(native):
+    # steps: +n allocates n bytes, -i releases the block of step i (1-based); 512-byte granules
+    offs, used, free_blocks = native._test_range_allocator(1 << 20, [1000, 512, 4096, -2, 300, -1, -3, -5, 1 << 20])
+    assert offs[0] == 0 and offs[1] == 1024 and offs[2] == 1536          # 1000 B takes two granules
+    assert offs[3] == 0                                                    # release of step 2's block
+    assert offs[4] == 1024                                                 # first fit: reuses the hole
+    assert offs[5:8] == [0, 0, 0] and used == 1 << 20 and free_blocks == 0  # all released, coalesced, whole range taken
+    assert offs[8] == 0
+    offs, used, _ = native._test_range_allocator(4096, [4096, 1, -1, -1])
+    assert offs == [0, -1, 0, -2] and used == 0                            # full -> -1; double release is refused
