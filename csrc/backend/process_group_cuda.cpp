@@ -633,9 +633,10 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allreduce(at::Tensor& t, c
         p.count = n;
         p.op = to_kern_op(op);
         p.scale = (op == c10d::ReduceOp::AVG ? 1.0f / ws : 1.0f) * prescale;
-        // each rank's SMs only move its own chunk (the switch does the fan-in and fan-out): a small grid
+        // each rank's SMs only move its own chunk (the switch does the fan-in and fan-out): a small grid.
+        // Measured on 4 ranks, 94 M MLP under DDP: 88.1 k samples/s with 16 CTAs, 86.9 k with 32, 81.6 k with 64.
         kern::LaunchCfg lc = cp.cfg(t.nbytes() / ws, overlapped);
-        lc.ctas = std::min<int>(lc.ctas, static_cast<int>(env_int("MCCL_NVLS_INPLACE_CTAS", 32)));
+        lc.ctas = std::min<int>(lc.ctas, static_cast<int>(env_int("MCCL_NVLS_INPLACE_CTAS", 16)));
         if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_allreduce_nvls_inplace(p, dt, lc, cp.stream.stream()));
         cp.algo = "nvls-inplace";
         const uint64_t sent = t.nbytes() + t.nbytes() / ws;

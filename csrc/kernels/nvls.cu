@@ -23,6 +23,8 @@
 //
 // Fills the role of the reference's bandwidth-optimal large-message path, the chunked ring
 // (reference csrc/backend/ProcessGroupMCCL.cpp:1712-1959).
+#include <cstdlib>
+
 #include "kernels/coll_common.cuh"
 
 namespace mccl {
@@ -364,6 +366,21 @@ __global__ void __launch_bounds__(512) nvls_inplace_kernel(const __grid_constant
   stamp(k, 6);
 }
 
+// Threads per CTA of the kernels that only do the link phase (in-place and split forms).  They hold
+// no shared memory and at most 128 registers per thread, so a 256-thread CTA takes half an SM's
+// register file and can share the SM with other kernels' CTAs (a staging pass of the other lane, a
+// backward GEMM) instead of waiting for a whole SM to drain.  MCCL_NVLS_THREADS overrides (128..512).
+int link_threads() {
+  static const int v = [] {
+    const char* e = std::getenv("MCCL_NVLS_THREADS");
+    int t = e ? std::atoi(e) : 256;
+    if (t < 128) t = 128;
+    if (t > 512) t = 512;
+    return t / 32 * 32;
+  }();
+  return v;
+}
+
 template <typename T, typename W>
 cudaError_t go_split(const CollParams& p, int ctas, const LaunchCfg& cfg, cudaStream_t s) {
   const int64_t units = (p.count + Unit<T, W>::N - 1) / Unit<T, W>::N;
@@ -373,7 +390,7 @@ cudaError_t go_split(const CollParams& p, int ctas, const LaunchCfg& cfg, cudaSt
   nvls_stage_in_kernel<T, W><<<copy_ctas, 512, 0, s>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  e = do_launch(nvls_reduce_bcast_kernel<T, W>, p, ctas, cfg.threads, 0, s);
+  e = do_launch(nvls_reduce_bcast_kernel<T, W>, p, ctas, link_threads(), 0, s);
   if (e != cudaSuccess) return e;
   nvls_stage_out_kernel<T, W><<<copy_ctas, 512, 0, s>>>(p);
   return cudaGetLastError();
@@ -406,9 +423,9 @@ cudaError_t launch_allreduce_nvls_inplace(const CollParams& p, DType dtype, Laun
   // each rank only moves its own chunk: size the grid for count / ws
   const size_t own_bytes = p.count * dtype_size(dtype) / p.ctx[0].ws;
   const int ctas = clamp_ctas(cfg.ctas > 0 ? cfg.ctas : pick_ctas(own_bytes, p.ctx[0].ws, 0), cfg);
-  if (dtype == F32) return do_launch(nvls_inplace_kernel<float>, p, ctas, cfg.threads, 0, s);
-  if (dtype == F16) return do_launch(nvls_inplace_kernel<__half>, p, ctas, cfg.threads, 0, s);
-  return do_launch(nvls_inplace_kernel<__nv_bfloat16>, p, ctas, cfg.threads, 0, s);
+  if (dtype == F32) return do_launch(nvls_inplace_kernel<float>, p, ctas, link_threads(), 0, s);
+  if (dtype == F16) return do_launch(nvls_inplace_kernel<__half>, p, ctas, link_threads(), 0, s);
+  return do_launch(nvls_inplace_kernel<__nv_bfloat16>, p, ctas, link_threads(), 0, s);
 }
 
 cudaError_t launch_allreduce_nvls(const CollParams& p, DType dtype, DType wire, LaunchCfg cfg, cudaStream_t s,

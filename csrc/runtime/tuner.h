@@ -53,14 +53,17 @@ class Tuner {
         // used from 5 ranks on, above the one-shot range.
         nvls_min_[ws][cls] = ws <= 4 ? kNever : (int64_t(1) << 20) + 1;
       }
-      // multimem.st also delivers a copy back to the sender, which costs 1/ws of the ingress: measured on
-      // 4 ranks the plain peer stores win at every size (1 GiB allgather: 1.37 ms vs 1.89 ms)
+      // multimem.st also delivers a copy back to the sender, which costs 1/ws of the ingress.  Measured on
+      // 4 ranks: for allgather (every rank sends) the plain peer stores win from 8 MiB up (256 MiB: 367 vs
+      // 474 us) and the two are within 2 us below; for broadcast (one sender, and one hop instead of two)
+      // multimem.st wins at every size from 16 KiB to 256 MiB (515 vs 662 us at 256 MiB).
       ag_nvls_min_[ws] = kNever;
-      bc_nvls_min_[ws] = kNever;
+      bc_nvls_min_[ws] = ws <= 2 ? kNever : (int64_t(16) << 10);
       ctas_small_[ws] = 32;
       ctas_large_[ws] = kern::kMaxCtasPerLane;  // two lanes may run at once: 2 x 64 CTAs stay below the 148 SMs
-      // measured on 2 ranks: 64 MiB 158 us pushed vs 185 us pulled (the stores overlap the reduction)
-      push_gather_[ws] = ws <= 2 ? 1 : 0;
+      // measured: 2 ranks 64 MiB 158 us pushed vs 185 us pulled (the stores overlap the reduction);
+      // 4 ranks 217 vs 234 us (32 MiB: 121 vs 133 us); 8 ranks equal within noise
+      push_gather_[ws] = ws <= 4 ? 1 : 0;
       // Gradient buckets run while backward GEMMs need the SMs.  Measured on 2 ranks (94 M MLP, DDP):
       // 73.7 k samples/s with 48 CTAs per allreduce, 71.1 k with 32, 71.2 k with 24, 67.3 k with 16,
       // 66.6 k with 64.  0 = same as ctas_large.

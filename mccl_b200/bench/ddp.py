@@ -31,6 +31,8 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--bucket-mb", type=int, default=25)
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (0: the config's default)")
+    ap.add_argument("--curve-points", type=int, default=10, help="how many points of the loss curve to print")
+    ap.add_argument("--optim-in-backward", action="store_true", help="AdamW per bucket behind its allreduce (native hook)")
     args = ap.parse_args(argv)
 
     rank, ws, local = (int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("WORLD_SIZE", "1"), ("LOCAL_RANK", "0")))
@@ -60,8 +62,12 @@ def main(argv=None):
             ids = torch.randint(0, vocab, (bs, seq + 1), device=dev)
             return ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
     n_params = sum(p.numel() for p in model.parameters())
+    pre_opt = None
     if args.impl == "mccl":
-        ddp = wrap_ddp(model, device_ids=[local], bucket_cap_mb=args.bucket_mb, compression=args.compression)
+        if args.optim_in_backward and args.model != "resnet50" and args.compression == "none":
+            pre_opt = FusedAdamW(model.parameters(), lr=1e-3 if args.model == "mlp" else 3e-4)
+        ddp = wrap_ddp(model, device_ids=[local], bucket_cap_mb=args.bucket_mb, compression=args.compression,
+                       optimizer_in_backward=pre_opt)
         if args.compression == "topk":
             ddp._mccl_topk_state.ratio = args.topk_ratio
     else:
@@ -70,6 +76,8 @@ def main(argv=None):
                                       gradient_as_bucket_view=True)
     if args.model == "resnet50":
         opt = torch.optim.SGD(ddp.parameters(), lr=0.1, momentum=0.9)
+    elif pre_opt is not None:
+        opt = pre_opt
     elif args.impl == "mccl":
         opt = FusedAdamW(ddp.parameters(), lr=1e-3 if args.model == "mlp" else 3e-4)
     else:
@@ -102,7 +110,7 @@ def main(argv=None):
         print(json.dumps({"bench": "ddp", "model": args.model, "impl": args.impl, "compression": args.compression,
                           "n_gpus": ws, "params": n_params, "per_gpu_batch": bs, "ms_per_step": round(ms, 3),
                           "samples_per_s": round(bs * ws / (ms / 1e3), 1), "dtype": "bf16 autocast" if autocast else "fp32",
-                          "losses": [round(float(l), 4) for l in losses[:: max(1, len(losses) // 10)]],
+                          "losses": [round(float(l), 4) for l in losses[:: max(1, len(losses) // max(1, args.curve_points))]],
                           "data": "synthetic"}), flush=True)
     dist.destroy_process_group()
     return 0

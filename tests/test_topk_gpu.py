@@ -38,6 +38,37 @@ def test_select_ties_take_lower_index(native, cuda_device):
     assert res.cpu().tolist() == [1.0, 0.0, 0.0, 0.0, -2.0, 0.5, 2.0, 0.0]
 
 
+@pytest.mark.parametrize("kind", ["few_magnitudes", "mostly_zero", "all_equal", "bf16_grid"])
+def test_select_on_heavily_tied_data_matches_host_oracle(native, cuda_device, kind):
+    # The chosen top-digit bin holds far more than k elements here, so the candidate list of the
+    # collect pass overflows and the full-vector refinement passes decide the threshold; the ties at
+    # the threshold must still go to the lowest indices, exactly like the host implementation.
+    n, ratio = 400_003, 0.02
+    gen = torch.Generator().manual_seed(11)
+    if kind == "few_magnitudes":
+        g = torch.randint(-3, 4, (n,), generator=gen).float()
+    elif kind == "mostly_zero":
+        g = torch.zeros(n)
+        nz = torch.randperm(n, generator=gen)[: n // 500]
+        g[nz] = torch.randn(n // 500, generator=gen)
+    elif kind == "all_equal":
+        g = torch.full((n,), -0.75)
+    else:
+        g = torch.randn(n, generator=gen).bfloat16().float().mul(8).round().div(8)   # coarse grid: many exact ties
+    comp, idx, val = _oracle_pairs(native, g, ratio)
+    res = torch.zeros(n, device=cuda_device)
+    pairs = native._topk_select(g.to(cuda_device), res, ratio)
+    torch.cuda.synchronize()
+    assert pairs[:, 0].cpu().tolist() == idx
+    assert pairs[:, 1].cpu().view(torch.float32).tolist() == val
+    assert torch.equal(res.cpu(), comp.residual(0))
+    # a second call on the same residual (now with holes where entries were sent) stays exact too
+    _, idx2, _ = _oracle_pairs(native, g, ratio, comp=comp)
+    pairs2 = native._topk_select(g.to(cuda_device), res, ratio)
+    assert pairs2[:, 0].cpu().tolist() == idx2
+    assert torch.equal(res.cpu(), comp.residual(0))
+
+
 def test_error_feedback_accumulates_like_oracle(native, cuda_device):
     n, ratio = 50_000, 0.02
     comp = native.TopKCompressor(ratio)
