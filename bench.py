@@ -221,6 +221,7 @@ def main():
                 last = float(last.item())
             return float(t.item()), clocks, launches, last
 
+        pooled = getattr(ddp, "_mccl_nvls_pool", None) is not None
         for i in range(warmup):
             train_step(dev_x[i % n_host_batches], dev_y[i % n_host_batches])
         ms_total, clocks, launches, _ = timed(args.steps, e2e=False)
@@ -230,7 +231,7 @@ def main():
         del ddp, opt, model
         torch.cuda.empty_cache()
         return {"ms_total": ms_total, "ms_e2e": ms_e2e, "clocks": clocks, "clocks_e2e": clocks_e2e,
-                "launches": launches, "final_loss": loss_b, "n_params": n_params, "in_bw": in_bw,
+                "launches": launches, "final_loss": loss_b, "n_params": n_params, "in_bw": in_bw, "pooled": pooled,
                 "value": GLOBAL_BATCH / (ms_total / args.steps / 1e3),
                 "e2e_value": GLOBAL_BATCH / (ms_e2e / args.steps / 1e3)}
 
@@ -297,6 +298,7 @@ def main():
             "fused_avg_hook": args.impl == "mccl" and not args.no_fused_hook,
             "fused_adamw": args.impl == "mccl" and not args.no_fused_optim,
             "optimizer_in_backward": args.impl == "mccl" and in_bw,
+            "nvls_in_place_buckets": args.impl == "mccl" and main_arm["pooled"],
         },
         "clocks": clocks,
         "e2e": {"value": round(e2e_value, 2), "unit": "samples/s", "ms_per_step": round(ms_e2e / args.steps, 4),

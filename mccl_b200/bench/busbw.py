@@ -40,13 +40,23 @@ def bus_factor(op: str, n: int) -> float:
     return 1.0
 
 
-def make_call(op, group, ws, rank, numel_total, dtype, dev, pool):
-    """Returns (list of zero-arg callables, payload bytes); one callable per pooled buffer."""
+def make_call(op, group, ws, rank, numel_total, dtype, dev, pool, mem_pool=None):
+    """Returns (list of zero-arg callables, payload bytes); one callable per pooled buffer.
+
+    ``mem_pool``: allocate the allreduce buffers from this ``torch.cuda.MemPool`` (multicast-bound
+    memory: the in-place NVLS kernel then runs instead of the staged ones).
+    """
     esz = torch.empty(0, dtype=dtype).element_size()
     calls = []
     if op == "allreduce":
         for _ in range(pool):
-            t = torch.randn(numel_total, device=dev).to(dtype)
+            src = torch.randn(numel_total, device=dev).to(dtype)
+            if mem_pool is not None:
+                with torch.cuda.use_mem_pool(mem_pool):
+                    t = torch.empty_like(src)
+                t.copy_(src)
+            else:
+                t = src
             calls.append(lambda t=t: dist.all_reduce(t, group=group))
         nbytes = numel_total * esz
     elif op == "broadcast":
@@ -278,7 +288,9 @@ def main(argv=None):
     ap.add_argument("--min-bytes", type=int, default=1024)
     ap.add_argument("--max-bytes", type=int, default=1 << 30)
     ap.add_argument("--compare-nccl", action="store_true")
-    ap.add_argument("--variants", default="", help="comma list of oneshot,twoshot,nvls: extra groups with the variant pinned")
+    ap.add_argument("--variants", default="",
+                    help="comma list of oneshot,twoshot,nvls (extra groups with the variant pinned) and pool "
+                         "(allreduce buffers allocated in multicast-bound memory on the default group: in-place NVLS)")
     ap.add_argument("--out", default="")
     ap.add_argument("--quick", action="store_true", help="every other size, fewer iterations")
     ap.add_argument("--tune", default="", help="measure every tuner crossover on this world size and write a tuner file here")
@@ -299,7 +311,16 @@ def main(argv=None):
         dist.destroy_process_group()
         return 0
     groups = {"mccl": None}
+    mem_pool = None
     for v in [x for x in args.variants.split(",") if x]:
+        if v == "pool":
+            from mccl_b200.parallel import nvls_tensor_pool
+            mem_pool = nvls_tensor_pool(min(3 << 30, 2 * args.max_bytes + (256 << 20)), device=dev)
+            if mem_pool is None and rank == 0:
+                print(json.dumps({"note": "no NVLS on this box: pool variant skipped"}), flush=True)
+            if mem_pool is not None:
+                groups["mccl-pool"] = None
+            continue
         g = pinned_group(v, nvls="1" if v == "nvls" else "0")
         if v == "nvls" and not has_nvls(g, dev):
             if rank == 0:
@@ -328,7 +349,10 @@ def main(argv=None):
                         continue
                     if gname == "mccl-twoshot" and op == "reduce_scatter":
                         continue  # reduce_scatter has one kernel: same as the default group
-                    calls, nbytes = make_call(op, group, ws, rank, numel, dtype, dev, pool)
+                    if gname == "mccl-pool" and op != "allreduce":
+                        continue
+                    calls, nbytes = make_call(op, group, ws, rank, numel, dtype, dev, pool,
+                                              mem_pool if gname == "mccl-pool" else None)
                     ms = time_calls(calls, iters, max(3, iters // 10), dev, groups["mccl"])
                     algbw = nbytes / (ms * 1e-3) / 1e9
                     row = {"op": op, "dtype": dname, "bytes": nbytes, "backend": gname, "n_gpus": ws,

@@ -136,6 +136,37 @@ def _install_native_bucket_hook(ddp, optimizer, process_group) -> None:
     ddp.register_forward_pre_hook(lambda _m, _inp: optimizer.sync_native_hook())
 
 
+def nvls_tensor_pool(nbytes: int, process_group=None, device=None):
+    """A ``torch.cuda.MemPool`` of ``nbytes`` of multicast-bound device memory, or None.
+
+    Tensors allocated inside ``with torch.cuda.use_mem_pool(pool):`` are reduced IN PLACE by the
+    NVSwitch when they are passed to ``all_reduce`` (SUM / AVG of fp32, fp16, bf16; byte length a
+    multiple of 16): no staging copies.  Collective: every rank calls it with the same size, and
+    every rank must then allocate the same sizes in the same order (a tensor has to sit at the same
+    offset on all ranks; the backend checks this the first time it sees a tensor and falls back to
+    the staged kernels otherwise).  One pool per device and process.  Returns None when the group
+    has no NVLS (``MCCL_NVLS=0``, no NVSwitch multicast, world size 1).
+    """
+    from .. import require_native
+
+    if os.environ.get("MCCL_NVLS", "auto") in ("0", "off") or not dist.is_initialized():
+        return None
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    device = torch.device(device)
+    backend = _backend_for(process_group, device)
+    if backend.size() < 2 or not hasattr(backend, "create_nvls_user_pool"):
+        return None
+    want = (int(nbytes) + (1 << 21) - 1) // (1 << 21) * (1 << 21)
+    if not backend.create_nvls_user_pool(want, device.index):
+        return None
+    native = require_native()
+    alloc = torch.cuda.memory.CUDAPluggableAllocator(native.__file__, "mccl_nvls_pool_alloc", "mccl_nvls_pool_free")
+    pool = torch.cuda.MemPool(alloc.allocator())
+    pool._mccl_allocator = alloc  # keep the ctypes handles alive as long as the pool
+    return pool
+
+
 def _nvls_bucket_pool(module: torch.nn.Module, process_group):
     """A ``torch.cuda.MemPool`` whose memory is bound to the group's NVLink multicast object, or None.
 
@@ -145,8 +176,6 @@ def _nvls_bucket_pool(module: torch.nn.Module, process_group):
     call it (``wrap_ddp`` does).  Returns None when NVLS is unavailable, switched off
     (``MCCL_NVLS=0`` / ``MCCL_NVLS_BUCKETS=0``) or the world size is 1.
     """
-    from .. import require_native
-
     if os.environ.get("MCCL_NVLS_BUCKETS", "1") == "0" or os.environ.get("MCCL_NVLS", "auto") in ("0", "off"):
         return None
     params = [p for p in module.parameters() if p.requires_grad]
@@ -163,14 +192,7 @@ def _nvls_bucket_pool(module: torch.nn.Module, process_group):
     # buckets are rebuilt once after the first backward, and a process may wrap a model more than once
     # before the first wrapper's memory is back: room for four generations plus slack
     want = int(os.environ.get("MCCL_NVLS_POOL_BYTES", "0")) or (4 * need + (256 << 20))
-    want = (want + (1 << 21) - 1) // (1 << 21) * (1 << 21)
-    if not backend.create_nvls_user_pool(want, device.index):
-        return None
-    native = require_native()
-    alloc = torch.cuda.memory.CUDAPluggableAllocator(native.__file__, "mccl_nvls_pool_alloc", "mccl_nvls_pool_free")
-    pool = torch.cuda.MemPool(alloc.allocator())
-    pool._mccl_allocator = alloc  # keep the ctypes handles alive as long as the pool
-    return pool
+    return nvls_tensor_pool(want, process_group, device)
 
 
 def wrap_ddp(module: torch.nn.Module, *, device_ids=None, bucket_cap_mb: Optional[int] = None,
