@@ -155,6 +155,9 @@ def tune(path, rank, ws, dev, max_bytes):
         dtype = DTYPES[dname]
         esz = 4 if dname == "fp32" else 2
         t_all = {}
+        for g in groups.values():  # first use of a group pays its one-time setup: keep it out of the table
+            calls, _ = make_call("allreduce", g, ws, rank, sizes[0] // esz, dtype, dev, 1)
+            time_calls(calls, 5, 3, dev, None)
         for size in sizes:
             pool, iters = pool_and_iters(size, quick=True)
             t = {}
@@ -170,13 +173,13 @@ def tune(path, rank, ws, dev, max_bytes):
             if rank == 0:
                 print(json.dumps(row), flush=True)
             torch.cuda.empty_cache()
+        # the largest size at which one-shot is not beaten (a single noisy row below it must not move
+        # the threshold: one-shot's advantage only grows downwards)
         best_one = 0
         for size in sizes:
             t = t_all[size]
             if "oneshot" in t and t["oneshot"] <= min(v for k, v in t.items() if k != "oneshot"):
                 best_one = size
-            else:
-                break
         table[f"ws{ws}_oneshot_max_bytes{key}"] = best_one
         nvls_min = -1
         if nvls:
