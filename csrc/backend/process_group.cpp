@@ -739,7 +739,8 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::allreduce_scaled(std::vector<at
 }
 
 c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::allreduce_scaled_then(std::vector<at::Tensor>& tensors, float scale,
-                                                                       std::function<void(cudaStream_t)> epilogue) {
+                                                                       std::function<void(cudaStream_t)> epilogue,
+                                                                       bool overlapped) {
   check_alive("allreduce_scaled_then");
   check_single(tensors, "allreduce_scaled_then");
   at::Tensor& t = tensors[0];
@@ -749,7 +750,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::allreduce_scaled_then(std::vect
     if (epilogue) epilogue(c10::cuda::getCurrentCUDAStream(t.device().index()).stream());
     return completed_work(c10d::OpType::ALLREDUCE, {t}, &t);
   }
-  return cuda_allreduce(t, c10d::ReduceOp::SUM, scale, std::move(epilogue), /*overlapped=*/true);
+  return cuda_allreduce(t, c10d::ReduceOp::SUM, scale, std::move(epilogue), overlapped);
 }
 
 c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::allreduce_coalesced(

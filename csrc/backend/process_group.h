@@ -116,8 +116,11 @@ class ProcessGroupMCCL : public c10d::Backend {
   c10::intrusive_ptr<c10d::Work> allreduce_scaled(std::vector<at::Tensor>& tensors, float scale);
   // Same, then `epilogue(stream)` is enqueued right behind the reduction on the communication
   // stream and covered by the returned Work (used to chain a bucket's optimizer kernel natively).
+  // `overlapped` = false tells the launcher that no compute is left to share the GPU with (the last
+  // bucket of a backward pass): the grid may then be larger than the one used under backward.
   c10::intrusive_ptr<c10d::Work> allreduce_scaled_then(std::vector<at::Tensor>& tensors, float scale,
-                                                        std::function<void(cudaStream_t)> epilogue);
+                                                        std::function<void(cudaStream_t)> epilogue,
+                                                        bool overlapped = true);
   // Collective: a pool of multicast-bound device memory for user tensors (see runtime/nvls_pool.h).
   bool create_nvls_user_pool(int64_t bytes, c10::DeviceIndex dev);
   // Test hook: next CUDA collective is skipped on this rank (peers must time out).

@@ -603,11 +603,14 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allreduce(at::Tensor& t, c
   cp.bus_factor = 2.0 * (ws - 1) / ws;
 
   // Tensor inside the multicast-bound pool (a DDP bucket built by wrap_ddp): reduce it in place, in
-  // the switch, with no staging and a grid sized for this rank's chunk only.
+  // the switch, with no staging and a grid sized for this rank's chunk only.  With two ranks the
+  // in-switch reduction moves as many bytes as the peer-memory kernels and measured slower at every
+  // size (256 MiB: 750 us against 499 us), so there it is used only when the threshold is set by hand.
+  const int64_t inplace_min = env_int("MCCL_NVLS_INPLACE_MIN_BYTES", ws <= 2 ? -1 : (1 << 20));
   if (cuda_->user_pool && wire == dt && kern::nvls_allreduce_supported(dt, dt, to_kern_op(op)) &&
       options_->algo != "oneshot" && options_->algo != "twoshot" && t.nbytes() % 16 == 0 &&
       (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0 &&
-      t.nbytes() >= static_cast<size_t>(env_int("MCCL_NVLS_INPLACE_MIN_BYTES", 1 << 20))) {
+      inplace_min >= 0 && t.nbytes() >= static_cast<size_t>(inplace_min)) {
     NvlsUserPool& pool = NvlsUserPool::get(dev);
     if (pool.active() && pool.contains(t.data_ptr(), t.nbytes())) {
       const size_t off = pool.offset_of(t.data_ptr());
@@ -635,8 +638,10 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::cuda_allreduce(at::Tensor& t, c
         p.scale = (op == c10d::ReduceOp::AVG ? 1.0f / ws : 1.0f) * prescale;
         // each rank's SMs only move its own chunk (the switch does the fan-in and fan-out): a small grid.
         // Measured on 4 ranks, 94 M MLP under DDP: 88.1 k samples/s with 16 CTAs, 86.9 k with 32, 81.6 k with 64.
+        // MCCL_NVLS_INPLACE_CTAS_ALONE: the grid when the caller says nothing overlaps (default: the same).
         kern::LaunchCfg lc = cp.cfg(t.nbytes() / ws, overlapped);
-        lc.ctas = std::min<int>(lc.ctas, static_cast<int>(env_int("MCCL_NVLS_INPLACE_CTAS", 16)));
+        const int64_t grid_cap = env_int("MCCL_NVLS_INPLACE_CTAS", 16);
+        lc.ctas = std::min<int>(lc.ctas, static_cast<int>(overlapped ? grid_cap : env_int("MCCL_NVLS_INPLACE_CTAS_ALONE", grid_cap)));
         if (!cp.skip) MCCL_LAUNCH_CHECK(kern::launch_allreduce_nvls_inplace(p, dt, lc, cp.stream.stream()));
         cp.algo = "nvls-inplace";
         const uint64_t sent = t.nbytes() + t.nbytes() / ws;

@@ -1,5 +1,5 @@
-// STFT / iSTFT kernels (sm_100a): shared-memory radix-2 FFTs of half the frame length (real
-// input / real output), several frames per CTA, twiddles computed once per CTA, with
+// STFT / iSTFT kernels (sm_100a): shared-memory radix-4 Stockham FFTs of half the frame length
+// (real input / real output), several frames per CTA, twiddles computed once per CTA, with
 // the padding, windowing and scaling fused into the loads and stores, and an
 // atomics-free gather overlap-add.  See stft_api.h for the decomposition.
 // Replaces the reference's one-thread-per-frame Metal FFT (reference
@@ -14,8 +14,6 @@ namespace mccl {
 namespace kern {
 
 namespace {
-
-__device__ __forceinline__ int bit_reverse(int x, int bits) { return __brev(static_cast<unsigned>(x)) >> (32 - bits); }
 
 __device__ __forceinline__ void fill_twiddles(float2* tw, int n) {
   for (int k = threadIdx.x; k < n / 2; k += blockDim.x) {
@@ -62,28 +60,64 @@ __device__ __forceinline__ float envelope_at(const float* window, int64_t p, int
 //   inverse:  Z[k] = (X[k] + conj X[h-k]) + i W_N^{-k} (X[k] - conj X[h-k]),  z = IFFT_h(Z) (no 1/h),
 //             y[2m] = Re z[m], y[2m+1] = Im z[m]   (y = unnormalised inverse of the Hermitian extension)
 
-// Radix-2 passes over `fpc` independent transforms of length h stored back to back in `data`
-// (bit-reversed order on entry).  tw[k] = exp(-2*pi*i*k/N) with N = 2h, so W_h^k = tw[2k].
-__device__ __forceinline__ void fft_half_smem(float2* data, const float2* tw, int h, int log2h, int fpc, float sign) {
-  const int per = h / 2;
-  for (int s = 1; s <= log2h; ++s) {
-    const int half = 1 << (s - 1);
-    const int tstep = (h >> s) * 2;
+// Stockham autosort FFT over `fpc` independent transforms of length h stored back to back
+// (natural order in, natural order out: no bit-reversal pass, whose shared-memory scatter would put
+// a whole warp on one bank).  Radix-4 passes (four values per thread in registers; an odd log2(h)
+// starts with one radix-2 pass) ping-pong between `a` and `b`; every pass reads at stride h/4 and
+// writes runs of Ns consecutive values.  tw[t] = exp(-2*pi*i*t/(2h)), t < h; tw[t + h] = -tw[t].
+// Returns the buffer that holds the result.
+__device__ __forceinline__ float2 cmul_tw(float2 v, float2 w, float conj_sign) {
+  // v * (w.x + i * conj_sign * w.y): conj_sign = +1 keeps the table's forward twiddle, -1 conjugates it
+  const float wy = conj_sign * w.y;
+  return make_float2(v.x * w.x - v.y * wy, v.x * wy + v.y * w.x);
+}
+
+__device__ __forceinline__ float2* fft_half_smem(float2* a, float2* b, const float2* tw, int h, int log2h, int fpc,
+                                                 float sign) {
+  const float cs = -sign;  // sign = -1: forward (table as stored); +1: inverse (conjugated)
+  float2* src = a;
+  float2* dst = b;
+  int ns = 1;
+  if (log2h & 1) {
+    const int per = h / 2;
     for (int jj = threadIdx.x; jj < per * fpc; jj += blockDim.x) {
-      const int f = jj / per, j = jj - f * per;
-      float2* d = data + f * h;
-      const int pos = j & (half - 1);
-      const int i0 = ((j >> (s - 1)) << s) + pos;
-      const int i1 = i0 + half;
-      float2 w = tw[pos * tstep];
-      w.y *= -sign;  // table holds the forward twiddle (negative angle)
-      const float2 a = d[i0], b = d[i1];
-      const float2 t = make_float2(b.x * w.x - b.y * w.y, b.x * w.y + b.y * w.x);
-      d[i0] = make_float2(a.x + t.x, a.y + t.y);
-      d[i1] = make_float2(a.x - t.x, a.y - t.y);
+      const int f = jj >> (log2h - 1), j = jj & (per - 1);
+      const float2 v0 = src[f * h + j], v1 = src[f * h + j + per];
+      float2* d = dst + f * h + 2 * j;
+      d[0] = make_float2(v0.x + v1.x, v0.y + v1.y);
+      d[1] = make_float2(v0.x - v1.x, v0.y - v1.y);
     }
     __syncthreads();
+    float2* t = src; src = dst; dst = t;
+    ns = 2;
   }
+  const int quarter = h / 4;
+  for (; ns < h; ns *= 4) {
+    const int tstep = h / (2 * ns);  // exp(-2*pi*i*r*k/(4*ns)) = tw[r * k * tstep]
+    for (int jj = threadIdx.x; jj < quarter * fpc; jj += blockDim.x) {
+      const int f = jj >> (log2h - 2), j = jj & (quarter - 1);
+      const int k = j & (ns - 1);
+      const int t1 = k * tstep, t3 = 3 * t1;
+      const float2* x = src + f * h + j;
+      float2 w3 = tw[t3 < h ? t3 : t3 - h];
+      if (t3 >= h) w3 = make_float2(-w3.x, -w3.y);
+      const float2 v0 = x[0];
+      const float2 v1 = cmul_tw(x[quarter], tw[t1], cs);
+      const float2 v2 = cmul_tw(x[2 * quarter], tw[2 * t1], cs);
+      const float2 v3 = cmul_tw(x[3 * quarter], w3, cs);
+      const float2 a0 = make_float2(v0.x + v2.x, v0.y + v2.y), a1 = make_float2(v0.x - v2.x, v0.y - v2.y);
+      const float2 a2 = make_float2(v1.x + v3.x, v1.y + v3.y), a3 = make_float2(v1.x - v3.x, v1.y - v3.y);
+      const float2 r3 = make_float2(cs * a3.y, -cs * a3.x);  // -i * a3 forward, +i * a3 inverse
+      float2* d = dst + f * h + ((j - k) << 2) + k;
+      d[0] = make_float2(a0.x + a2.x, a0.y + a2.y);
+      d[ns] = make_float2(a1.x + r3.x, a1.y + r3.y);
+      d[2 * ns] = make_float2(a0.x - a2.x, a0.y - a2.y);
+      d[3 * ns] = make_float2(a1.x - r3.x, a1.y - r3.y);
+    }
+    __syncthreads();
+    float2* t = src; src = dst; dst = t;
+  }
+  return src;
 }
 
 __device__ __forceinline__ float load_sample(const FftFramesArgs& a, const float* sig, int64_t t, int n) {
@@ -104,7 +138,8 @@ __global__ void __launch_bounds__(256) fft_frames_kernel(const FftFramesArgs a, 
   extern __shared__ float2 smem[];
   const int n = a.n_fft, h = n / 2;
   float2* tw = smem;        // h twiddles W_N^k
-  float2* data = smem + h;  // fpc * h values
+  float2* data = smem + h;  // fpc * h values, and as many again for the ping-pong passes
+  float2* pong = data + fpc * h;
   const int b = blockIdx.y;
   fill_twiddles(tw, n);
   const float* sig = a.signal + static_cast<int64_t>(b) * a.signal_len;
@@ -112,34 +147,47 @@ __global__ void __launch_bounds__(256) fft_frames_kernel(const FftFramesArgs a, 
   for (int f0 = blockIdx.x * fpc; f0 < a.n_frames; f0 += gridDim.x * fpc) {
     __syncthreads();  // twiddles ready / previous frames' bins written
     for (int jj = threadIdx.x; jj < h * fpc; jj += blockDim.x) {
-      const int f = jj / h, m = jj - f * h;
+      const int f = jj >> log2h, m = jj & (h - 1);
       const int frame = f0 + f;
       float v0 = 0.f, v1 = 0.f;
       if (frame < a.n_frames) {
         const int64_t start = static_cast<int64_t>(frame) * a.hop - a.pad;
-        v0 = load_sample(a, sig, start + 2 * m, n) * a.window[2 * m];
-        v1 = load_sample(a, sig, start + 2 * m + 1, n) * a.window[2 * m + 1];
+        const int64_t t0 = start + 2 * m;
+        if (a.reflect && start >= 0 && start + n <= a.signal_len) {  // frame inside the signal: no index folding
+          v0 = sig[t0];
+          v1 = sig[t0 + 1];
+        } else {
+          v0 = load_sample(a, sig, t0, n);
+          v1 = load_sample(a, sig, t0 + 1, n);
+        }
+        v0 *= a.window[2 * m];
+        v1 *= a.window[2 * m + 1];
       }
-      data[f * h + bit_reverse(m, log2h)] = make_float2(v0, v1);
+      data[jj] = make_float2(v0, v1);
     }
     __syncthreads();
-    fft_half_smem(data, tw, h, log2h, fpc, -1.0f);
-    for (int jj = threadIdx.x; jj < bins * fpc; jj += blockDim.x) {
-      const int f = jj / bins, k = jj - f * bins;
+    const float2* res = fft_half_smem(data, pong, tw, h, log2h, fpc, -1.0f);
+    for (int jj = threadIdx.x; jj < h * fpc; jj += blockDim.x) {
+      const int f = jj >> log2h, k = jj & (h - 1);
       const int frame = f0 + f;
       if (frame >= a.n_frames) continue;
-      const float2* d = data + f * h;
-      const float2 zk = d[k == h ? 0 : k];
+      const float2* d = res + f * h;
+      const float2 zk = d[k];
       const float2 zm = d[(h - k) & (h - 1)];            // Z[h-k], with Z[h] = Z[0]
       const float2 e = make_float2(0.5f * (zk.x + zm.x), 0.5f * (zk.y - zm.y));
       const float2 o = make_float2(0.5f * (zk.y + zm.y), -0.5f * (zk.x - zm.x));   // (Zk - conj Zm) / (2i)
-      const float2 w = k == h ? make_float2(-1.f, 0.f) : tw[k];
+      const float2 w = tw[k];
       float2 v = make_float2(e.x + w.x * o.x - w.y * o.y, e.y + w.x * o.y + w.y * o.x);
       float sc = a.scale;
-      if (a.hermitian_weights && k != 0 && k != h) sc *= 2.0f;
-      if (a.hermitian_weights && (k == 0 || k == h)) v.y = 0.f;  // imaginary parts of DC/Nyquist are ignored by an inverse real FFT
+      if (a.hermitian_weights && k != 0) sc *= 2.0f;
+      if (a.hermitian_weights && k == 0) v.y = 0.f;  // imaginary parts of DC/Nyquist are ignored by an inverse real FFT
       float2* out = reinterpret_cast<float2*>(a.out) + (static_cast<int64_t>(b) * a.n_frames + frame) * bins;
       out[k] = make_float2(v.x * sc, v.y * sc);
+      if (k == 0) {  // Nyquist bin: X[h] = E[0] - O[0] (twiddle -1), from the same Z[0]
+        float2 vn = make_float2(e.x - o.x, e.y - o.y);
+        if (a.hermitian_weights) vn.y = 0.f;
+        out[h] = make_float2(vn.x * a.scale, vn.y * a.scale);
+      }
     }
   }
 }
@@ -149,6 +197,7 @@ __global__ void __launch_bounds__(256) ifft_frames_kernel(const IfftFramesArgs a
   const int n = a.n_fft, h = n / 2;
   float2* tw = smem;
   float2* data = smem + h;
+  float2* pong = data + fpc * h;
   const int b = blockIdx.y;
   fill_twiddles(tw, n);
   // hermitian: inverse real FFT of the one-sided bins.  Otherwise the adjoint of the forward
@@ -159,7 +208,7 @@ __global__ void __launch_bounds__(256) ifft_frames_kernel(const IfftFramesArgs a
   for (int f0 = blockIdx.x * fpc; f0 < a.n_frames; f0 += gridDim.x * fpc) {
     __syncthreads();
     for (int jj = threadIdx.x; jj < h * fpc; jj += blockDim.x) {
-      const int f = jj / h, k = jj - f * h;
+      const int f = jj >> log2h, k = jj & (h - 1);
       const int frame = f0 + f;
       float2 z = make_float2(0.f, 0.f);
       if (frame < a.n_frames) {
@@ -176,15 +225,15 @@ __global__ void __launch_bounds__(256) ifft_frames_kernel(const IfftFramesArgs a
         const float2 od = make_float2(dm.x * w.x - dm.y * w.y, dm.x * w.y + dm.y * w.x);
         z = make_float2(ep.x - od.y, ep.y + od.x);                 // E' + i O'
       }
-      data[f * h + bit_reverse(k, log2h)] = z;
+      data[jj] = z;
     }
     __syncthreads();
-    fft_half_smem(data, tw, h, log2h, fpc, +1.0f);
+    const float2* res = fft_half_smem(data, pong, tw, h, log2h, fpc, +1.0f);
     for (int jj = threadIdx.x; jj < h * fpc; jj += blockDim.x) {
-      const int f = jj / h, m = jj - f * h;
+      const int f = jj >> log2h, m = jj & (h - 1);
       const int frame = f0 + f;
       if (frame >= a.n_frames) continue;
-      const float2 v = data[f * h + m];
+      const float2 v = res[jj];
       float2* out = reinterpret_cast<float2*>(a.frames + (static_cast<int64_t>(b) * a.n_frames + frame) * n);
       out[m] = make_float2(v.x * post * a.window[2 * m], v.y * post * a.window[2 * m + 1]);
     }
@@ -238,7 +287,7 @@ bool valid_nfft(int n) { return n >= 8 && n <= kStftMaxNfft && (n & (n - 1)) == 
 // every thread butterflies, enough CTAs to fill the GPU a few times over, each looping over frames.
 void frame_grid(int n_fft, int n_frames, int batch, int* fpc, int* grid_x, size_t* smem) {
   const int h = n_fft / 2;
-  int f = 512 / h;  // 256 threads, h/2 butterflies per frame and stage
+  int f = 2048 / h;  // 256 threads, h/4 radix-4 groups per frame and pass: two groups per thread
   if (f < 1) f = 1;
   if (f > 8) f = 8;
   *fpc = f;
@@ -246,7 +295,7 @@ void frame_grid(int n_fft, int n_frames, int batch, int* fpc, int* grid_x, size_
   int64_t cap = (148 * 8 + batch - 1) / batch;
   if (cap < 1) cap = 1;
   *grid_x = static_cast<int>(want < cap ? want : cap);
-  *smem = (static_cast<size_t>(h) + static_cast<size_t>(f) * h) * sizeof(float2);
+  *smem = (static_cast<size_t>(h) + 2 * static_cast<size_t>(f) * h) * sizeof(float2);  // <= 48 KB at n_fft 4096
 }
 
 }  // namespace

@@ -3,7 +3,7 @@
 // Two kernels cover forward and backward of both transforms:
 //   frames -> spectrum  (fft_frames):  one CTA per (batch, frame) loads n_fft
 //       samples (reflect padding or an envelope division fused into the load),
-//       multiplies by the window, runs a shared-memory radix-2 FFT and writes
+//       multiplies by the window, runs a shared-memory radix-4 Stockham FFT and writes
 //       the n_fft/2+1 one-sided bins.
 //   spectrum -> frames  (ifft_frames): one CTA per (batch, frame) loads the
 //       one-sided bins (Hermitian-extended for an inverse real FFT, or

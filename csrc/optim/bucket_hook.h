@@ -25,6 +25,7 @@
 #include <vector>
 
 #include "backend/process_group.h"
+#include "common/env.h"
 #include "optim/adamw_plan.h"
 
 namespace mccl {
@@ -130,9 +131,13 @@ class BucketOptimizerHook : public c10d::CommHookInterface {
     const float scale = static_cast<float>(st.scale);
     lk.unlock();
     std::vector<at::Tensor> v{bucket.getBufferRef()};
+    // the last bucket of a backward pass has no backward kernels left to share the GPU with
+    // (MCCL_LAST_BUCKET_ALONE=1 lets its allreduce use the larger, non-overlapped grid)
+    static const bool last_alone = env_int("MCCL_LAST_BUCKET_ALONE", 0) != 0;
+    const bool overlapped = !(last_alone && bucket.isLast());
     auto work = st.pg->allreduce_scaled_then(v, scale, [launches, step](cudaStream_t s) {
       for (const auto& l : launches) l.plan->launch(s, l.h.lr, l.h.beta1, l.h.beta2, l.h.eps, l.h.weight_decay, step, 1.0);
-    });
+    }, overlapped);
     return work->getFuture();
   }
 

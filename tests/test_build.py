@@ -35,3 +35,11 @@ def test_import_mccl_alias():
     assert mccl.get_metrics() is None  # no process group yet
     assert mccl.staging_pool_bytes() >= 0
     mccl.log_metrics(); mccl.reset_metrics(); mccl.trim_staging_pool()
+
+
+def test_nvls_tensor_pool_is_none_without_a_group_or_when_switched_off(monkeypatch):
+    # the public helper never raises where NVLS cannot exist: no process group, or MCCL_NVLS=0
+    from mccl_b200.parallel import nvls_tensor_pool
+    assert nvls_tensor_pool(1 << 20) is None
+    monkeypatch.setenv("MCCL_NVLS", "0")
+    assert nvls_tensor_pool(1 << 20) is None

@@ -274,7 +274,8 @@ def test_nvls_in_place_allreduce_on_pool_tensors_and_ddp_buckets(ws):
     if ws > _ngpu():
         pytest.skip("not enough GPUs")
     res = run_workers(_inplace_worker, ws, device="cuda", timeout=300,
-                      env={"MCCL_NVLS": "1", "MCCL_LOG_LEVEL": "INFO", "MCCL_DEVICE_TIMING": "1", "MCCL_NVLS_BUCKETS_MIN_WORLD": "2"})
+                      env={"MCCL_NVLS": "1", "MCCL_LOG_LEVEL": "INFO", "MCCL_DEVICE_TIMING": "1", "MCCL_NVLS_BUCKETS_MIN_WORLD": "2",
+                           "MCCL_NVLS_INPLACE_MIN_BYTES": "1048576"})
     _skip_if_unavailable(res)
     if "NVLS_UNAVAILABLE" not in res[0].stdout:
         assert "algo=nvls-inplace" in res[0].stderr, res[0].stderr[-2000:]
