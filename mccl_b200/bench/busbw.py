@@ -84,7 +84,7 @@ def make_call(op, group, ws, rank, numel_total, dtype, dev, pool, mem_pool=None)
 
 
 def time_calls(calls, iters, warmup, dev, sync_group):
-    for i in range(warmup):
+    for i in range(max(warmup, len(calls))):  # every buffer once: first use of a buffer may do one-time setup
         calls[i % len(calls)]()
     torch.cuda.synchronize()
     dist.barrier(group=sync_group)
