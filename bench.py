@@ -14,7 +14,10 @@ CUDA events (max over ranks):
   value  K full training steps (forward, backward with bucketed gradient allreduce,
          optimizer step) on device-resident inputs;
   e2e    K steps through the same public API where every step also copies its inputs from
-         pinned host memory to the device and reads the loss back to the host.
+         pinned host memory to the device and reads the loss back to the host
+         (``mccl_b200.utils.data``: the copy of batch i+1 is enqueued behind step i on a side
+         stream, and step i-1's loss is read while step i is being launched; the last loss is
+         read before the clock stops; the same loop drives every arm).
 ``--impl mccl`` (default) is this framework: backend "mccl", DDP gradient buckets in
 multicast-bound memory reduced in place by the NVSwitch (4 ranks and more), the native
 allreduce + AdamW bucket hook (more than one rank), fused AdamW kernel.  After the headline arm
@@ -139,6 +142,7 @@ def main():
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
 
     from mccl_b200.models import MLP94M, num_parameters
+    from mccl_b200.utils.data import AsyncScalarReader, DevicePrefetcher
 
     local_batch = GLOBAL_BATCH // world
     assert local_batch * world == GLOBAL_BATCH, "global batch 256 must divide by the world size"
@@ -198,12 +202,21 @@ def main():
             t0 = time.perf_counter()
             start.record()
             last = None
-            for i in range(region_steps):
-                if e2e:
-                    x = host_x[i % n_host_batches].to(dev, non_blocking=True)
-                    y = host_y[i % n_host_batches].to(dev, non_blocking=True)
-                    last = train_step(x, y).item()  # device -> host read of the step's result
-                else:
+            if e2e:
+                # every step: its inputs come from pinned host memory (copy of batch i+1 behind step i) and
+                # its loss is read on the host (step i-1's while step i is being launched; the last one
+                # before the clock stops)
+                feed = DevicePrefetcher(((host_x[i % n_host_batches], host_y[i % n_host_batches])
+                                         for i in range(region_steps)), dev)
+                losses = AsyncScalarReader(dev)
+                for i in range(region_steps):
+                    x, y = feed.next()
+                    losses.push(train_step(x, y))
+                    if i > 0:
+                        last = losses.pop()
+                last = losses.pop()
+            else:
+                for i in range(region_steps):
                     last = train_step(dev_x[i % n_host_batches], dev_y[i % n_host_batches])
             end.record()
             torch.cuda.synchronize()

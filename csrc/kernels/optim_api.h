@@ -32,7 +32,9 @@ struct AdamWHyper {
   float grad_scale;      // multiplied into every gradient first
 };
 
-cudaError_t launch_adamw_multi(const AdamWTable& tab, const AdamWHyper& h, cudaStream_t s);
+// `max_ctas` > 0 caps the grid (each CTA then walks several chunks): a step that runs beside other
+// kernels (a bucket's update during backward) can be kept to a share of the SMs and of HBM bandwidth.
+cudaError_t launch_adamw_multi(const AdamWTable& tab, const AdamWHyper& h, cudaStream_t s, int max_ctas = 0);
 
 }  // namespace kern
 }  // namespace mccl

@@ -96,7 +96,7 @@ class AdamWPlan {
   }
 
   void launch(cudaStream_t stream, double lr, double beta1, double beta2, double eps, double weight_decay,
-              int64_t step, double grad_scale) {
+              int64_t step, double grad_scale, int max_ctas = 0) {
     kern::AdamWTable tab;
     tab.params = reinterpret_cast<const uint64_t*>(d_p_.data_ptr<int64_t>());
     tab.grads = reinterpret_cast<const uint64_t*>(d_g_.data_ptr<int64_t>());
@@ -116,7 +116,7 @@ class AdamWPlan {
     h.step_size = static_cast<float>(lr / bc1);
     h.inv_sqrt_bias2 = static_cast<float>(1.0 / std::sqrt(bc2));
     h.grad_scale = static_cast<float>(grad_scale);
-    MCCL_PLAN_CK(kern::launch_adamw_multi(tab, h, stream));
+    MCCL_PLAN_CK(kern::launch_adamw_multi(tab, h, stream, max_ctas));
   }
   int num_chunks() const { return num_chunks_; }
 

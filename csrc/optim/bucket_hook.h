@@ -135,8 +135,14 @@ class BucketOptimizerHook : public c10d::CommHookInterface {
     // (MCCL_LAST_BUCKET_ALONE=1 lets its allreduce use the larger, non-overlapped grid)
     static const bool last_alone = env_int("MCCL_LAST_BUCKET_ALONE", 0) != 0;
     const bool overlapped = !(last_alone && bucket.isLast());
-    auto work = st.pg->allreduce_scaled_then(v, scale, [launches, step](cudaStream_t s) {
-      for (const auto& l : launches) l.plan->launch(s, l.h.lr, l.h.beta1, l.h.beta2, l.h.eps, l.h.weight_decay, step, 1.0);
+    // A bucket's update runs beside the rest of backward: MCCL_OIB_ADAMW_CTAS caps its grid so that it
+    // takes a share of the SMs and of HBM bandwidth instead of all of both (0 = no cap).  The last
+    // bucket has nothing beside it and always runs uncapped.
+    static const int capped = static_cast<int>(env_int("MCCL_OIB_ADAMW_CTAS", 0));
+    const int max_ctas = bucket.isLast() ? 0 : capped;
+    auto work = st.pg->allreduce_scaled_then(v, scale, [launches, step, max_ctas](cudaStream_t s) {
+      for (const auto& l : launches)
+        l.plan->launch(s, l.h.lr, l.h.beta1, l.h.beta2, l.h.eps, l.h.weight_decay, step, 1.0, max_ctas);
     }, overlapped);
     return work->getFuture();
   }
