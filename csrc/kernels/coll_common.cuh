@@ -229,6 +229,21 @@ struct TilePlan {
   }
 };
 
+// Tile size of a byte mover.  With more than four ranks a rank's share per CTA is small, and one
+// tile per CTA would serialise the two stages of the mover (push, then copy out or forward); such a
+// share is cut into about four tiles of at least 64 KiB.  Measured on 8 ranks: a 128 MiB two-hop
+// broadcast took 325 us with one 290 KB tile per CTA and slice (hop 1 then hop 2: no overlap).
+// Depends only on (units, grid, tile_bytes, ws), so it is the same on every rank.
+__host__ __device__ inline int64_t mover_tile_bytes(int64_t units, int nctas, int64_t tile_bytes, int ws) {
+  int64_t tb = tile_bytes > 0 ? tile_bytes : (128 << 10);
+  if (ws <= 4) return tb;
+  const int64_t per_cta_bytes = (units + nctas - 1) / nctas * 16;
+  if (per_cta_bytes >= 2 * tb) return tb;
+  int64_t quarter = per_cta_bytes / 4;
+  if (quarter < (64 << 10)) quarter = 64 << 10;
+  return quarter < tb ? quarter : tb;
+}
+
 __device__ __forceinline__ void stamp(const CtaCtx& k, int slot) {
   if (k.c->stamps != nullptr && k.cta == 0 && k.tid == 0) k.c->stamps[slot] = globaltimer_ns();
 }

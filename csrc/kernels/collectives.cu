@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(512) allgather_kernel(const __grid_constant__ 
   const int64_t units = (nbytes + 15) / 16;
   const size_t slot_bytes = round_up(static_cast<size_t>(units) * 16, 128);
   if (!range_ok(k, 0, slot_bytes * c.ws, stage_capacity<kMC>(k), 10)) return;
-  const TilePlan tp = TilePlan::make(units, k.nctas, k.nthreads, p.tile_bytes);
+  const TilePlan tp = TilePlan::make(units, k.nctas, k.nthreads, mover_tile_bytes(units, k.nctas, p.tile_bytes, c.ws));
   const int64_t my_tiles = tp.count_for(k.cta, k.nctas);
   const char* stage = stage_local<kMC>(k);
   const bool in_al = is_aligned16(in);
@@ -204,7 +204,8 @@ __global__ void __launch_bounds__(512) broadcast_kernel(const __grid_constant__ 
   // ---- two hops ------------------------------------------------------------------------------
   const int ns = c.ws - 1;
   const int64_t slice_units = (units + ns - 1) / ns;
-  const TilePlan tp = TilePlan::make(slice_units, k.nctas, k.nthreads, p.tile_bytes);
+  const TilePlan tp = TilePlan::make(slice_units, k.nctas, k.nthreads,
+                                     mover_tile_bytes(slice_units, k.nctas, p.tile_bytes, c.ws));
   const int64_t my_tiles = tp.count_for(k.cta, k.nctas);
   auto slice_base = [&](int q) -> int64_t { return static_cast<int64_t>(q < root ? q : q - 1) * slice_units; };
   if (c.rank == root) {

@@ -59,6 +59,10 @@ class Tuner {
       // multimem.st wins at every size from 16 KiB to 256 MiB (515 vs 662 us at 256 MiB).
       ag_nvls_min_[ws] = kNever;
       bc_nvls_min_[ws] = ws <= 2 ? kNever : (int64_t(16) << 10);
+      // Measured on 8 ranks: multimem.st wins up to 8 MiB (1 MiB: 17.6 vs 29.2 us, 8 MiB: 36.7 vs 43.2 us)
+      // and loses from 16 MiB up (64 MiB: 186 vs 161 us): one sender's multicast stores run near
+      // 385 GB/s there, below what the two-hop peer stores reach.  No ceiling at 3-4 ranks.
+      bc_nvls_max_[ws] = ws >= 5 ? (int64_t(8) << 20) : kNever;
       ctas_small_[ws] = 32;
       ctas_large_[ws] = kern::kMaxCtasPerLane;  // two lanes may run at once: 2 x 64 CTAs stay below the 148 SMs
       // measured: 2 ranks 64 MiB 158 us pushed vs 185 us pulled (the stores overlap the reduction);
@@ -86,7 +90,8 @@ class Tuner {
   }
   bool broadcast_nvls(int ws, size_t bytes) const {
     ws = clamp_ws(ws);
-    return bc_nvls_min_[ws] >= 0 && static_cast<int64_t>(bytes) >= bc_nvls_min_[ws];
+    return bc_nvls_min_[ws] >= 0 && static_cast<int64_t>(bytes) >= bc_nvls_min_[ws] &&
+           (bc_nvls_max_[ws] < 0 || static_cast<int64_t>(bytes) <= bc_nvls_max_[ws]);
   }
   size_t oneshot_max_bytes(int ws, int cls = 0) const { return static_cast<size_t>(oneshot_max_[clamp_ws(ws)][cls ? 1 : 0]); }
   void set_oneshot_max_bytes(int ws, size_t v) { oneshot_max_[ws][0] = oneshot_max_[ws][1] = static_cast<int64_t>(v); }
@@ -134,6 +139,7 @@ class Tuner {
       if (find_int(s, p + "nvls_min_bytes_16bit", v) && v >= -1) { nvls_min_[ws][1] = v; ++applied; }
       if (find_int(s, p + "allgather_nvls_min_bytes", v) && v >= -1) { ag_nvls_min_[ws] = v; ++applied; }
       if (find_int(s, p + "broadcast_nvls_min_bytes", v) && v >= -1) { bc_nvls_min_[ws] = v; ++applied; }
+      if (find_int(s, p + "broadcast_nvls_max_bytes", v) && v >= -1) { bc_nvls_max_[ws] = v; ++applied; }
       if (find_int(s, p + "ctas_small", v) && v > 0) { ctas_small_[ws] = static_cast<int>(v); ++applied; }
       if (find_int(s, p + "ctas_large", v) && v > 0) { ctas_large_[ws] = static_cast<int>(std::min<long long>(v, kern::kMaxCtasPerLane)); ++applied; }
       if (find_int(s, p + "push_gather", v) && v >= 0) { push_gather_[ws] = v ? 1 : 0; ++applied; }
@@ -157,6 +163,7 @@ class Tuner {
       o << p << "nvls_min_bytes_16bit\": " << nvls_min_[ws][1] << ", ";
       o << p << "allgather_nvls_min_bytes\": " << ag_nvls_min_[ws] << ", ";
       o << p << "broadcast_nvls_min_bytes\": " << bc_nvls_min_[ws] << ", ";
+      o << p << "broadcast_nvls_max_bytes\": " << bc_nvls_max_[ws] << ", ";
       o << p << "ctas_small\": " << ctas_small_[ws] << ", ";
       o << p << "ctas_large\": " << ctas_large_[ws] << ", ";
       o << p << "push_gather\": " << push_gather_[ws] << ", ";
@@ -189,6 +196,7 @@ class Tuner {
   int64_t nvls_min_[kern::kMaxWorld + 1][2];
   int64_t ag_nvls_min_[kern::kMaxWorld + 1];
   int64_t bc_nvls_min_[kern::kMaxWorld + 1];
+  int64_t bc_nvls_max_[kern::kMaxWorld + 1];  // -1: no ceiling
   int ctas_small_[kern::kMaxWorld + 1];
   int ctas_large_[kern::kMaxWorld + 1];
   int push_gather_[kern::kMaxWorld + 1];

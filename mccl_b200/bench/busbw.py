@@ -208,11 +208,17 @@ def tune(path, rank, ws, dev, max_bytes):
                 if rank == 0:
                     print(json.dumps(row), flush=True)
                 torch.cuda.empty_cache()
+            if op == "broadcast":
+                # one sender: multimem.st can win at small sizes and lose at large ones, so the table
+                # holds a floor and a ceiling (the smallest and the largest size at which it won)
+                wins = [size for size in sizes if t_all[size]["nvls"] <= t_all[size]["unicast"]]
+                table[f"ws{ws}_{field}"] = wins[0] if wins else -1
+                table[f"ws{ws}_broadcast_nvls_max_bytes"] = -1 if (not wins or wins[-1] == sizes[-1]) else wins[-1]
+                continue
             m = -1
             for size in reversed(sizes):
                 if t_all[size]["nvls"] <= t_all[size]["unicast"]:
-                    # allgather's threshold is per-rank bytes
-                    m = size // ws if op == "allgather" else size
+                    m = size // ws  # allgather's threshold is per-rank bytes
                 else:
                     break
             table[f"ws{ws}_{field}"] = m
