@@ -66,8 +66,8 @@ class Tuner {
       ctas_small_[ws] = 32;
       ctas_large_[ws] = kern::kMaxCtasPerLane;  // two lanes may run at once: 2 x 64 CTAs stay below the 148 SMs
       // measured: 2 ranks 64 MiB 158 us pushed vs 185 us pulled (the stores overlap the reduction);
-      // 4 ranks 217 vs 234 us (32 MiB: 121 vs 133 us); 8 ranks equal within noise
-      push_gather_[ws] = ws <= 4 ? 1 : 0;
+      // 4 ranks 217 vs 234 us (32 MiB: 121 vs 133 us); 8 ranks 247 vs 255 us (32 MiB: 137 vs 145 us)
+      push_gather_[ws] = 1;
       // Gradient buckets run while backward GEMMs need the SMs.  Measured on 2 ranks (94 M MLP, DDP):
       // 73.7 k samples/s with 48 CTAs per allreduce, 71.1 k with 32, 71.2 k with 24, 67.3 k with 16,
       // 66.6 k with 64.  0 = same as ctas_large.

@@ -60,7 +60,7 @@ def test_tuner_file_overrides(native, tmp_path, monkeypatch):
     assert t["ws8_oneshot_max_bytes"] == 524288 and t["ws8_ctas_large"] == 48 and t["segment_bytes"] == 33554432
     assert t["ws2_oneshot_max_bytes"] == 32 << 20   # untouched default
     assert t["ws8_push_gather"] == 1 and t["ws2_push_gather"] == 0
-    assert t["ws4_push_gather"] == 1   # untouched default (measured: owners push at up to 4 ranks)
+    assert t["ws4_push_gather"] == 1 and t["ws6_push_gather"] == 1   # untouched defaults (measured: owners push)
     assert t["ws8_ctas_overlap"] == 40 and t["ws2_ctas_overlap"] == 48 and t["ws4_ctas_overlap"] == 0
     pg.shutdown()
 
