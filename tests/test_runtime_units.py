@@ -53,6 +53,7 @@ def test_tuner_file_overrides(native, tmp_path, monkeypatch):
     f = tmp_path / "tune.json"
     f.write_text(json.dumps({"ws8_oneshot_max_bytes": 524288, "ws8_ctas_large": 48, "segment_bytes": 33554432,
                              "ws8_push_gather": 1, "ws2_push_gather": 0, "ws8_ctas_overlap": 40,
+                             "ws8_broadcast_nvls_min_bytes": 65536, "ws8_broadcast_nvls_max_bytes": 4194304,
                              "measured": [{"bytes": 1, "oneshot_us": 2.0}]}))
     monkeypatch.setenv("MCCL_TUNE_FILE", str(f))
     pg = native._create_process_group(dist.HashStore(), 0, 1, datetime.timedelta(seconds=10))
@@ -62,6 +63,9 @@ def test_tuner_file_overrides(native, tmp_path, monkeypatch):
     assert t["ws8_push_gather"] == 1 and t["ws2_push_gather"] == 0
     assert t["ws4_push_gather"] == 1 and t["ws6_push_gather"] == 1   # untouched defaults (measured: owners push)
     assert t["ws8_ctas_overlap"] == 40 and t["ws2_ctas_overlap"] == 48 and t["ws4_ctas_overlap"] == 0
+    # broadcast through multimem.st has a floor and a ceiling (no ceiling at 3-4 ranks by default)
+    assert t["ws8_broadcast_nvls_min_bytes"] == 65536 and t["ws8_broadcast_nvls_max_bytes"] == 4194304
+    assert t["ws6_broadcast_nvls_max_bytes"] == 8 << 20 and t["ws4_broadcast_nvls_max_bytes"] == -1
     pg.shutdown()
 
 
