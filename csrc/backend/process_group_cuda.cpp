@@ -187,7 +187,7 @@ void ProcessGroupMCCL::ensure_cuda(c10::DeviceIndex dev) {
     }
   }
   const auto timeout = std::chrono::milliseconds(env_int("MCCL_CONNECT_TIMEOUT_MS", 30000));
-  // Round 1: publish handles (or the reason there is none).
+  // First exchange: publish handles (or the reason there is none).
   std::string mine = st->arena ? ("H" + st->arena->export_handle()) : ("X" + local_reason);
   auto all = rendezvous_->exchange("arena", mine, timeout);
   if (local_reason.empty()) {
@@ -201,13 +201,13 @@ void ProcessGroupMCCL::ensure_cuda(c10::DeviceIndex dev) {
     }
     if (local_reason.empty()) local_reason = st->arena->open_peers(handles);
   }
-  // Round 2: agree. One failure anywhere puts every rank on the host-staged path.
-  auto verdicts = rendezvous_->exchange("arena_ok", local_reason.empty() ? "ok" : local_reason, timeout);
+  // Second exchange: agree. One failure anywhere puts every rank on the host-staged path.
+  auto answers = rendezvous_->exchange("arena_ok", local_reason.empty() ? "ok" : local_reason, timeout);
   st->p2p = true;
   for (int r = 0; r < ws; ++r)
-    if (verdicts[r] != "ok") {
+    if (answers[r] != "ok") {
       st->p2p = false;
-      st->why_not = "rank " + std::to_string(r) + ": " + verdicts[r];
+      st->why_not = "rank " + std::to_string(r) + ": " + answers[r];
       break;
     }
   if (!st->p2p) {

@@ -218,7 +218,7 @@ std::unique_ptr<NvlsRegion> NvlsRegion::create(int rank, int ws, size_t buffer_b
     return nullptr;
   };
 
-  // ---- round 0: local capability + rank 0's unique id for the socket names ---------------------
+  // ---- exchange 0: local capability + rank 0's unique id for the socket names ---------------------
   std::string e;
   if (!device_supported(&e)) { /* e set */ }
   if (e.empty()) e = im.d.load();
@@ -245,7 +245,7 @@ std::unique_ptr<NvlsRegion> NvlsRegion::create(int rank, int ws, size_t buffer_b
   }
   auto sock_name = [&](int r) { return "mccl-nvls-" + uid + "-" + std::to_string(r); };
 
-  // ---- round 1: sockets bound everywhere; rank 0 creates and exports the multicast object ------
+  // ---- exchange 1: sockets bound everywhere; rank 0 creates and exports the multicast object ------
   CUmulticastObjectProp prop;
   std::memset(&prop, 0, sizeof(prop));
   prop.numDevices = static_cast<unsigned>(ws);
@@ -298,7 +298,7 @@ std::unique_ptr<NvlsRegion> NvlsRegion::create(int rank, int ws, size_t buffer_b
     }
   }
 
-  // ---- round 2: the handle reaches every rank; every rank adds its device -----------------------
+  // ---- exchange 2: the handle reaches every rank; every rank adds its device -----------------------
   if (rank == 0) {
     for (int r = 1; r < ws && e.empty(); ++r)
       if (!send_fd(sock, sock_name(r), export_fd)) e = std::string("sending the multicast handle to rank ") + std::to_string(r) + ": " + std::strerror(errno);
@@ -325,7 +325,7 @@ std::unique_ptr<NvlsRegion> NvlsRegion::create(int rank, int ws, size_t buffer_b
     if (!bad.empty()) return fail(bad);
   }
 
-  // ---- round 3: physical memory, bind, map ------------------------------------------------------
+  // ---- exchange 3: physical memory, bind, map ------------------------------------------------------
   {
     CUresult r = im.d.MemCreate(&im.mem_handle, im.total, &aprop, 0);
     if (r != CUDA_SUCCESS) e = im.d.err("cuMemCreate", r);
