@@ -676,6 +676,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     kern::tile_plan_host(units, nctas, nthreads, tile_bytes, &tu, &nt);
     return std::make_pair(tu, nt);
   }, py::arg("units"), py::arg("nctas"), py::arg("nthreads") = 512, py::arg("tile_bytes") = 0);
+  m.def("_mover_tile_bytes", &kern::mover_tile_bytes_host, py::arg("units"), py::arg("nctas"), py::arg("tile_bytes") = 0,
+        py::arg("ws") = 2);
   m.attr("MAX_CTAS_PER_LANE") = kern::kMaxCtasPerLane;
 
   // ---- top-k kernels ------------------------------------------------------------------------

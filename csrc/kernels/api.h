@@ -114,6 +114,9 @@ size_t broadcast_stage_bytes(size_t nbytes);
 size_t nvls_allreduce_stage_bytes(size_t nbytes_wire, int ws);
 // Tile geometry the pipelined kernels derive for (units, grid); exposed for host-side checks.
 void tile_plan_host(int64_t units, int nctas, int nthreads, int64_t tile_bytes, int64_t* tile_units, int64_t* ntiles);
+// The tile size the byte movers (allgather, two-hop broadcast) use for `units` 16-byte units of one
+// rank's block on `nctas` CTAs at world size `ws` (test hook for the rule in coll_common.cuh).
+int64_t mover_tile_bytes_host(int64_t units, int nctas, int64_t tile_bytes, int ws);
 
 // All launchers return cudaSuccess or the launch error; none synchronises.
 // dtype: element type of in/out.  wire: element type stored in the arena

@@ -343,6 +343,10 @@ cudaError_t launch_broadcast(const CollParams& p, LaunchCfg cfg, cudaStream_t s)
   return do_launch(broadcast_kernel<false>, p, ctas, cfg.threads, cfg.emulate_ranks, s);
 }
 
+int64_t mover_tile_bytes_host(int64_t units, int nctas, int64_t tile_bytes, int ws) {
+  return mover_tile_bytes(units, nctas, tile_bytes, ws);
+}
+
 void tile_plan_host(int64_t units, int nctas, int nthreads, int64_t tile_bytes, int64_t* tile_units, int64_t* ntiles) {
   const TilePlan t = TilePlan::make(units, nctas, nthreads, tile_bytes);
   *tile_units = t.tile_units;

@@ -103,3 +103,23 @@ def test_pool_range_allocator_first_fit_and_coalescing(native):
     assert offs[8] == 0
     offs, used, _ = native._test_range_allocator(4096, [4096, 1, -1, -1])
     assert offs == [0, -1, 0, -2] and used == 0                            # full -> -1; double release is refused
+
+
+def test_mover_tile_rule_keeps_small_world_sizes_and_cuts_small_shares(native):
+    MiB, KiB = 1 << 20, 1 << 10
+    # up to four ranks: the configured tile, whatever the share per CTA
+    for ws in (2, 3, 4):
+        for units in (1, 10_000, 2_000_000):
+            assert native._mover_tile_bytes(units, 64, MiB, ws) == MiB
+            assert native._mover_tile_bytes(units, 64, 0, ws) == 128 * KiB
+    # more ranks: a share below two tiles per CTA is cut into about four tiles of at least 64 KiB
+    units = (32 * MiB) // 16                     # 32 MiB block on 64 CTAs = 512 KiB per CTA
+    assert native._mover_tile_bytes(units, 64, MiB, 8) == 128 * KiB
+    assert native._mover_tile_bytes(units // 16, 64, MiB, 8) == 64 * KiB      # small share: the floor
+    assert native._mover_tile_bytes(units * 8, 64, MiB, 8) == MiB             # 4 MiB per CTA: the configured tile
+    # whatever the tile, the plan stays a partition with tile g owned by CTA g % nctas
+    for ws in (5, 8):
+        for u in (4097, 300_000, 2_400_000):
+            tb = native._mover_tile_bytes(u, 64, MiB, ws)
+            tu, nt = native._tile_plan(u, 64, 512, tb)
+            assert tu > 0 and (nt - 1) * tu < u <= nt * tu
