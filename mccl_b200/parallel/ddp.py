@@ -230,8 +230,12 @@ def wrap_ddp(module: torch.nn.Module, *, device_ids=None, bucket_cap_mb: Optiona
             # DDP re-buckets once, at the start of the second iteration: make the new buckets come
             # from the same memory (its own call right after this one then finds nothing to do)
             if not state["rebuilt"] and torch.is_grad_enabled():
+                rebuild = getattr(ddp.reducer, "_rebuild_buckets", None)
+                if rebuild is None:  # a torch without this entry point: DDP's own rebuild then leaves the
+                    state["rebuilt"] = True  # pool, and the backend falls back to its staged kernels
+                    return
                 with torch.cuda.use_mem_pool(pool):
-                    if ddp.reducer._rebuild_buckets():
+                    if rebuild():
                         state["rebuilt"] = True
 
         ddp.register_forward_pre_hook(_rebuild_in_pool)
