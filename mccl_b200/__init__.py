@@ -51,9 +51,11 @@ def _load_native():
         except Exception as e:
             _native_error = e
             return None
+    import importlib
     try:
-        from . import _C  # type: ignore[attr-defined]
-        return _C
+        # import_module, not `from . import _C`: on a reload of this package the old module-level
+        # name `_C` (None after a failed first import) would be found and returned instead
+        return importlib.import_module(__name__ + "._C")
     except ImportError as first:
         building_now = "mccl_b200._build" in getattr(sys, "orig_argv", [])
         if os.environ.get("MCCL_NO_AUTOBUILD") == "1" or building_now:
@@ -66,8 +68,7 @@ def _load_native():
             return None
         try:
             _build.build()
-            from . import _C  # type: ignore[attr-defined]
-            return _C
+            return importlib.import_module(__name__ + "._C")
         except Exception as e:  # pragma: no cover - depends on the toolchain
             _native_error = e
             return None

@@ -43,3 +43,18 @@ def test_nvls_tensor_pool_is_none_without_a_group_or_when_switched_off(monkeypat
     assert nvls_tensor_pool(1 << 20) is None
     monkeypatch.setenv("MCCL_NVLS", "0")
     assert nvls_tensor_pool(1 << 20) is None
+
+
+def test_package_reload_imports_the_library_again(native):
+    # `from . import _C` would return the stale module-level name on a reload; the loader has to
+    # import the submodule itself (the build entry point reloads the package after compiling)
+    import importlib
+    import mccl_b200
+    saved = mccl_b200._C
+    try:
+        mccl_b200._C = None          # what a first import without the library leaves behind
+        importlib.reload(mccl_b200)
+        assert mccl_b200._C is not None and mccl_b200.require_native().__protocol_version__ == 5
+    finally:
+        if mccl_b200._C is None:
+            mccl_b200._C = saved
