@@ -22,7 +22,17 @@ namespace kern {
 
 namespace {
 
-__global__ void __launch_bounds__(256) adamw_multi_kernel(const AdamWTable tab, AdamWHyper h) {
+__device__ __forceinline__ void adamw_chunk(const AdamWTable& tab, const AdamWHyper& h, int chunk) {
+  const int2 ent = tab.chunks[chunk];
+  const int t = ent.x;
+  const int64_t start = static_cast<int64_t>(ent.y) * kAdamWChunk;
+  const int64_t n = tab.sizes[t];
+  int64_t end = start + kAdamWChunk;
+  if (end > n) end = n;
+  float* __restrict__ p = reinterpret_cast<float*>(tab.params[t]);
+  const float* __restrict__ g = reinterpret_cast<const float*>(tab.grads[t]);
+  float* __restrict__ m = reinterpret_cast<float*>(tab.exp_avg[t]);
+  float* __restrict__ v = reinterpret_cast<float*>(tab.exp_avg_sq[t]);
   const float decay = 1.0f - h.lr * h.weight_decay;
   const float one_m_b1 = 1.0f - h.beta1, one_m_b2 = 1.0f - h.beta2;
 
@@ -35,42 +45,40 @@ __global__ void __launch_bounds__(256) adamw_multi_kernel(const AdamWTable tab, 
     pp -= h.step_size * (mm / denom);
   };
 
-  // one chunk per CTA when the grid covers the table, several when the launcher capped the grid
-  for (int c = blockIdx.x; c < tab.num_chunks; c += gridDim.x) {
-    const int2 ent = tab.chunks[c];
-    const int t = ent.x;
-    const int64_t start = static_cast<int64_t>(ent.y) * kAdamWChunk;
-    const int64_t n = tab.sizes[t];
-    int64_t end = start + kAdamWChunk;
-    if (end > n) end = n;
-    float* __restrict__ p = reinterpret_cast<float*>(tab.params[t]);
-    const float* __restrict__ g = reinterpret_cast<const float*>(tab.grads[t]);
-    float* __restrict__ m = reinterpret_cast<float*>(tab.exp_avg[t]);
-    float* __restrict__ v = reinterpret_cast<float*>(tab.exp_avg_sq[t]);
-    const bool vec_ok = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) |
-                          reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15) == 0;
-    if (vec_ok) {
-      // chunk starts are multiples of 4, so 16-byte alignment carries over
-      const int64_t nvec = (end - start) / 4;
-      float4* p4 = reinterpret_cast<float4*>(p + start);
-      const float4* g4 = reinterpret_cast<const float4*>(g + start);
-      float4* m4 = reinterpret_cast<float4*>(m + start);
-      float4* v4 = reinterpret_cast<float4*>(v + start);
-      for (int64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
-        float4 pp = p4[i], gg = __ldcs(g4 + i), mm = m4[i], vv = v4[i];
-        update(pp.x, gg.x, mm.x, vv.x);
-        update(pp.y, gg.y, mm.y, vv.y);
-        update(pp.z, gg.z, mm.z, vv.z);
-        update(pp.w, gg.w, mm.w, vv.w);
-        p4[i] = pp;
-        m4[i] = mm;
-        v4[i] = vv;
-      }
-      for (int64_t i = start + nvec * 4 + threadIdx.x; i < end; i += blockDim.x) update(p[i], g[i], m[i], v[i]);
-    } else {
-      for (int64_t i = start + threadIdx.x; i < end; i += blockDim.x) update(p[i], g[i], m[i], v[i]);
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) |
+                        reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15) == 0;
+  if (vec_ok) {
+    // chunk starts are multiples of 4, so 16-byte alignment carries over
+    const int64_t nvec = (end - start) / 4;
+    float4* p4 = reinterpret_cast<float4*>(p + start);
+    const float4* g4 = reinterpret_cast<const float4*>(g + start);
+    float4* m4 = reinterpret_cast<float4*>(m + start);
+    float4* v4 = reinterpret_cast<float4*>(v + start);
+    for (int64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+      float4 pp = p4[i], gg = __ldcs(g4 + i), mm = m4[i], vv = v4[i];
+      update(pp.x, gg.x, mm.x, vv.x);
+      update(pp.y, gg.y, mm.y, vv.y);
+      update(pp.z, gg.z, mm.z, vv.z);
+      update(pp.w, gg.w, mm.w, vv.w);
+      p4[i] = pp;
+      m4[i] = mm;
+      v4[i] = vv;
     }
+    for (int64_t i = start + nvec * 4 + threadIdx.x; i < end; i += blockDim.x) update(p[i], g[i], m[i], v[i]);
+  } else {
+    for (int64_t i = start + threadIdx.x; i < end; i += blockDim.x) update(p[i], g[i], m[i], v[i]);
   }
+}
+
+// One chunk per CTA: the grid covers the table.
+__global__ void __launch_bounds__(256) adamw_multi_kernel(const AdamWTable tab, AdamWHyper h) {
+  adamw_chunk(tab, h, blockIdx.x);
+}
+
+// The launcher capped the grid: every CTA walks several chunks (a separate kernel so that the
+// uncapped step keeps its register count and occupancy).
+__global__ void __launch_bounds__(256) adamw_multi_capped_kernel(const AdamWTable tab, AdamWHyper h) {
+  for (int c = blockIdx.x; c < tab.num_chunks; c += gridDim.x) adamw_chunk(tab, h, c);
 }
 
 }  // namespace
@@ -78,8 +86,10 @@ __global__ void __launch_bounds__(256) adamw_multi_kernel(const AdamWTable tab, 
 cudaError_t launch_adamw_multi(const AdamWTable& tab, const AdamWHyper& h, cudaStream_t s, int max_ctas) {
   if (tab.num_chunks <= 0) return cudaSuccess;
   note_launch();
-  const int grid = max_ctas > 0 && max_ctas < tab.num_chunks ? max_ctas : tab.num_chunks;
-  adamw_multi_kernel<<<grid, 256, 0, s>>>(tab, h);
+  if (max_ctas > 0 && max_ctas < tab.num_chunks)
+    adamw_multi_capped_kernel<<<max_ctas, 256, 0, s>>>(tab, h);
+  else
+    adamw_multi_kernel<<<tab.num_chunks, 256, 0, s>>>(tab, h);
   return cudaGetLastError();
 }
 
