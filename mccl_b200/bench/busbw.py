@@ -130,6 +130,35 @@ def pool_and_iters(nbytes, quick=False):
     return pool, iters
 
 
+def oneshot_ceiling(sizes, t_all):
+    """The largest size at which one-shot is not beaten by any other variant (0: never).
+
+    A single noisy row below it must not move the threshold: one-shot's advantage only grows downwards.
+    """
+    best = 0
+    for size in sizes:
+        t = t_all[size]
+        others = [v for k, v in t.items() if k != "oneshot"]
+        if "oneshot" in t and others and t["oneshot"] <= min(others):
+            best = size
+    return best
+
+
+def nvls_floor(sizes, t_all, above):
+    """The smallest size > ``above`` from which NVLS beats two-shot in all rows but at most one (-1: never).
+
+    One lost row inside a range that NVLS otherwise wins (a noisy measurement) does not push the floor
+    above that range; two lost rows do.
+    """
+    cand = [s for s in sizes if s > above and "nvls" in t_all[s] and "twoshot" in t_all[s]]
+    for i, s in enumerate(cand):
+        rest = cand[i:]
+        lost = sum(1 for r in rest if t_all[r]["nvls"] > t_all[r]["twoshot"])
+        if t_all[s]["nvls"] <= t_all[s]["twoshot"] and lost <= (1 if len(rest) >= 4 else 0):
+            return s
+    return -1
+
+
 def tune(path, rank, ws, dev, max_bytes):
     """Measures, for this world size, every choice the tuner table holds and writes a tuner file.
 
@@ -173,22 +202,11 @@ def tune(path, rank, ws, dev, max_bytes):
             if rank == 0:
                 print(json.dumps(row), flush=True)
             torch.cuda.empty_cache()
-        # the largest size at which one-shot is not beaten (a single noisy row below it must not move
-        # the threshold: one-shot's advantage only grows downwards)
-        best_one = 0
-        for size in sizes:
-            t = t_all[size]
-            if "oneshot" in t and t["oneshot"] <= min(v for k, v in t.items() if k != "oneshot"):
-                best_one = size
+        best_one = oneshot_ceiling(sizes, t_all)
         table[f"ws{ws}_oneshot_max_bytes{key}"] = best_one
         nvls_min = -1
         if nvls:
-            for size in reversed(sizes):
-                t = t_all[size]
-                if t["nvls"] <= t["twoshot"]:
-                    nvls_min = size
-                else:
-                    break
+            nvls_min = nvls_floor(sizes, t_all, best_one)
             if nvls_min >= 0:
                 nvls_min = max(nvls_min, best_one + 1)
         table[f"ws{ws}_nvls_min_bytes{key}"] = nvls_min
