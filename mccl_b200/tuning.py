@@ -22,13 +22,14 @@ def apply_thunderbolt_production_defaults(*, training_defaults: bool = False) ->
 def apply_nvlink_production_defaults(*, training_defaults: bool = False) -> None:
     """CUDA data-plane preset for an 8x B200 NVSwitch node.
 
-    Collectives run on the side stream (overlap on) with the tuner's size table;
-    with ``training_defaults`` DDP buckets are sized so that one bucket is one
-    two-shot segment (launch latency amortised, still several buckets in flight
-    for a ~100 M parameter model).
+    Collectives run on the side streams (overlap on) with the tuner's size table and the NVLS
+    kernels where the switch offers multicast; with ``training_defaults`` DDP buckets are sized
+    so that one bucket is one segment (launch latency amortised, still several buckets in
+    flight for a ~100 M parameter model).
     """
     os.environ.setdefault("MCCL_OVERLAP_COMM", "1")
     os.environ.setdefault("MCCL_ALGO", "auto")
+    os.environ.setdefault("MCCL_NVLS", "auto")
     if training_defaults:
         os.environ.setdefault("DDP_BUCKET_MB", "64")
 
